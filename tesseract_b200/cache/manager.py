@@ -62,19 +62,19 @@ class CacheManager:
         self.slots = StateSlots(max_requests)
         self.scratch_slot = max_requests       # one state slot more than requests: padded rows point here
         self.groups: List[_Group] = []
-        self._group_of_entry: List[Optional[int]] = [None] * len(needs)
-        self._index_in_group: List[Optional[int]] = [None] * len(needs)
+        # per run entry: (group, index in the group's storage) of each of its needs (one, or several for a tuple)
+        self._places: List[List[Tuple[int, int]]] = [[] for _ in needs]
         by_need: Dict[object, int] = {}
-        for entry, need in enumerate(needs):
-            if need is None:
+        for entry, entry_need in enumerate(needs):
+            if entry_need is None:
                 continue
-            if need not in by_need:
-                by_need[need] = len(self.groups)
-                self.groups.append(_Group(need=need, entries=[]))
-            group = by_need[need]
-            self._group_of_entry[entry] = group
-            self._index_in_group[entry] = len(self.groups[group].entries)
-            self.groups[group].entries.append(entry)
+            for need in (entry_need if isinstance(entry_need, tuple) else (entry_need,)):
+                if need not in by_need:
+                    by_need[need] = len(self.groups)
+                    self.groups.append(_Group(need=need, entries=[]))
+                group = by_need[need]
+                self._places[entry].append((group, len(self.groups[group].entries)))
+                self.groups[group].entries.append(entry)
         for group in self.groups:
             need = group.need
             if isinstance(need, PagedNeed):
@@ -93,14 +93,18 @@ class CacheManager:
         self.bindings: List[Optional[CacheBinding]] = []
         for entry, need in enumerate(needs):
             source = entry if cache_of[entry] is None else cache_of[entry]
-            group = self._group_of_entry[source]
-            if group is None:
+            made = []
+            for group, index in self._places[source]:
+                g = self.groups[group]
+                storage = g.storage[index] if g.storage is not None else None
+                made.append(CacheBinding(group=group, storage=storage, writes=cache_of[entry] is None,
+                                         page_size=page_size if g.pool is not None else 0))
+            if not made:
                 self.bindings.append(None)
-                continue
-            g = self.groups[group]
-            storage = g.storage[self._index_in_group[source]] if g.storage is not None else None
-            self.bindings.append(CacheBinding(group=group, storage=storage, writes=cache_of[entry] is None,
-                                              page_size=page_size if g.pool is not None else 0))
+            elif isinstance(needs[source], tuple):
+                self.bindings.append(tuple(made))
+            else:
+                self.bindings.append(made[0])
         self._requests: Dict[Hashable, _Request] = {}
         self.pages_reused = 0          # pages handed out that an earlier owner had given back
         self._ever_used: List[set] = [set() for _ in self.groups]
@@ -109,9 +113,9 @@ class CacheManager:
     def pages_for(self, group: _Group, tokens: int) -> int:
         """Peak pages a request of ``tokens`` tokens holds in ``group`` at any one time."""
         total = -(-tokens // self.page_size)
-        window = getattr(group.need, "window", None)
-        if window:
-            live = -(-(window - 1 + self.max_step_tokens) // self.page_size) + 1
+        span = group.need.live_span()
+        if span is not None:
+            live = -(-(span + self.max_step_tokens) // self.page_size) + 1
             return min(total, live)
         return total
 
@@ -196,7 +200,7 @@ class CacheManager:
         state = self._requests[request]
         state.length += new_tokens
         for index, g in enumerate(self.groups):
-            if g.pool is None or not getattr(g.need, "window", None):
+            if g.pool is None or g.need.live_span() is None:
                 continue
             first_needed = self._first_needed_page(g, state.length)
             held = state.pages[index]
@@ -221,10 +225,7 @@ class CacheManager:
 
     def _first_needed_page(self, group: _Group, next_position: int) -> int:
         """Lowest logical page that a query at ``next_position`` or later can still read."""
-        window = getattr(group.need, "window", None)
-        if not window:
-            return 0
-        return max(0, next_position - window + 1) // self.page_size
+        return group.need.first_needed_position(next_position) // self.page_size
 
     # ------------------------------------------------------------------ views
     def block_table_rows(self, group_index: int, slots: Sequence[int], columns: int) -> np.ndarray:

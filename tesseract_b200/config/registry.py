@@ -1,7 +1,7 @@
 """The one registry from an architecture's name to its model.
 
-``config.json``'s ``architectures[0]`` selects the entry, as the reference's loader does
-(src/model/mod.rs:91-111); a missing name and an unknown name are two distinct errors
+``config.json``'s ``architectures[0]`` (or, where that list is absent, the string ``architecture``) selects the
+entry, as the reference's loader does (src/model/mod.rs:91-111); a missing name and an unknown name are two distinct errors
 (src/model/mod.rs:190-202).  An entry knows how to read its typed configuration and how
 to turn it into an architecture-neutral :class:`ModelSpec`; everything after that is
 shared.
@@ -12,7 +12,7 @@ from __future__ import annotations
 import importlib
 import os
 from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, Iterable, List, Mapping, Sequence, Tuple
+from typing import Any, Callable, Dict, Iterable, List, Mapping, Optional, Sequence, Tuple
 
 from .reading import NoArchitectureError, UnsupportedArchitectureError, read_config_json
 from .spec import ModelSpec
@@ -24,6 +24,9 @@ class Architecture:
     read_config: Callable[[Mapping[str, Any]], Any]
     build_spec: Callable[[Any], ModelSpec]
     ignorable_tensors: Callable[[Any], Iterable[str]] = lambda cfg: ()
+    # (typed configuration, run dtype name) -> the kernel files a model of this architecture calls, or None: the
+    # package's default list for the dtype.  Loading a model compiles these, side by side, and no others.
+    kernel_libraries: Optional[Callable[[Any, str], Iterable[str]]] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -59,6 +62,8 @@ def load_plugins(modules: Sequence[str] = ()) -> None:
 
 def resolve_architecture(config: Mapping[str, Any]) -> Architecture:
     names = config.get("architectures") or []
+    if not names and isinstance(config.get("architecture"), str):
+        names = [config["architecture"]]          # some designs name themselves with one string
     if not names:
         raise NoArchitectureError("config.json names no architecture ('architectures' is missing or empty)")
     first = names[0]

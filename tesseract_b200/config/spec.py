@@ -52,15 +52,16 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block: ``block`` arranges ``norms``, ``mixer`` and ``feed_forward``."""
+    """One block: ``block`` arranges ``norms``, ``mixer`` and ``feed_forward`` (None: a layer that ends after its
+    mixer, if the block kind allows it)."""
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     norms_items: Tuple[Tuple[str, PartSpec], ...]
 
     @classmethod
-    def make(cls, block: str, mixer: PartSpec, feed_forward: PartSpec,
+    def make(cls, block: str, mixer: PartSpec, feed_forward: Optional[PartSpec],
              norms: Mapping[str, PartSpec]) -> "LayerSpec":
         return cls(block, mixer, feed_forward, tuple(sorted(norms.items())))
 

@@ -50,6 +50,10 @@ SOURCES: Dict[str, List[str]] = {
     "gemm_tcgen05": [],
     "skinny_tcgen05": [],
     "sampling": [],
+    "polynorm": [],
+    "conv_rope_cache": [],
+    "attention_masked": [],
+    "gated_recurrence": [],
 }
 
 

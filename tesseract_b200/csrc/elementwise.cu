@@ -102,6 +102,27 @@ TB_EXPORT int tb_embedding(const int* tokens, const void* table, void* out, int 
     return gather_rows(tokens, table, out, rows, hidden, vocab, dtype, stream);
 }
 
+namespace {
+
+// out[t, :] = float(table[token[t], :]): a bfloat16 table feeding a residual stream that is kept in 32-bit.
+__global__ void embedding_widen_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
+                                       float* __restrict__ out, int hidden, int vocab) {
+    int from = tokens[blockIdx.x];
+    if (from < 0 || from >= vocab) from = 0;
+    const __nv_bfloat16* s = table + (int64_t)from * hidden;
+    float* d = out + (int64_t)blockIdx.x * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) d[i] = __bfloat162float(s[i]);
+}
+
+}  // namespace
+
+TB_EXPORT int tb_embedding_widen(const int* tokens, const void* table, float* out, int rows, int hidden, int vocab,
+                                 cudaStream_t stream) {
+    if (rows == 0) return 0;
+    embedding_widen_kernel<<<rows, 256, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out, hidden, vocab);
+    return tb_launch_status();
+}
+
 TB_EXPORT int tb_gather_rows(const int* rows_index, const void* in, void* out, int rows, int width,
                              int num_in_rows, int dtype, cudaStream_t stream) {
     return gather_rows(rows_index, in, out, rows, width, num_in_rows, dtype, stream);

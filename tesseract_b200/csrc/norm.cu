@@ -10,6 +10,11 @@
 // else a loop over the row; the kernel and block size are chosen from the width alone, so that a row's result
 // does not depend on the batch around it.  The weight vector
 // is always 32-bit (a bfloat16 checkpoint vector is widened exactly at load).
+//
+//   tb_group_rms_norm  the same norm taken over `groups` equal consecutive parts of a row, each with its own
+//                      statistic, for a residual stream kept in 32-bit: c = res [+ upd]; res_out = c (32-bit);
+//                      y[part] = round(c[part] * rsqrt(mean(c[part]^2) + eps) * w[part]).  The update and the
+//                      output each have a type of their own (32-bit or bfloat16).  groups = 1 is the plain norm.
 #include "common.cuh"
 
 namespace {
@@ -167,5 +172,73 @@ TB_EXPORT int tb_add_rms_norm(const void* res, const void* upd, const float* w, 
                               int width, float eps, int dtype, cudaStream_t stream) {
     if (dtype == TB_F32) return launch<float, true>(res, upd, w, y, res_out, rows, width, eps, stream);
     if (dtype == TB_BF16) return launch<__nv_bfloat16, true>(res, upd, w, y, res_out, rows, width, eps, stream);
+    return TB_ERR_BAD_DTYPE;
+}
+
+namespace {
+
+// One block per (row, group): a row of `groups` parts is `groups` rows of the part's width whose weights repeat
+// with period `groups`.  The block size follows from the part's width alone.
+template <typename U, typename T, bool ADD>
+__global__ void group_rms_norm_kernel(const float* __restrict__ res, const U* __restrict__ upd,
+                                      const float* __restrict__ w, T* __restrict__ y, float* __restrict__ res_out,
+                                      int part, int groups, float eps) {
+    extern __shared__ __align__(16) float part_cache[];
+    __shared__ float scratch[32];
+    const int64_t base = (int64_t)blockIdx.x * part;
+    const float* wp = w + (int64_t)(blockIdx.x % groups) * part;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < part; j += blockDim.x) {
+        float v = res[base + j];
+        if (ADD) {
+            v += Elem<U>::load(upd + base + j);
+            res_out[base + j] = v;
+        }
+        part_cache[j] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)part + eps);
+    for (int j = threadIdx.x; j < part; j += blockDim.x) Elem<T>::store(y + base + j, part_cache[j] * inv * wp[j]);
+}
+
+template <typename U, typename T>
+int launch_group(const float* res, const void* upd, const float* w, void* y, float* res_out, int rows, int width,
+                 int groups, float eps, cudaStream_t stream) {
+    const int part = width / groups;
+    const size_t smem = (size_t)part * sizeof(float);
+    if (smem > 200 * 1024) return TB_ERR_BAD_SIZE;
+    int threads = 32;
+    while (threads < 512 && threads * 4 < part) threads <<= 1;
+    const dim3 grid((unsigned)((int64_t)rows * groups));
+    if (upd != nullptr) {
+        auto kernel = group_rms_norm_kernel<U, T, true>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<grid, threads, smem, stream>>>(res, (const U*)upd, w, (T*)y, res_out, part, groups, eps);
+    } else {
+        auto kernel = group_rms_norm_kernel<U, T, false>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<grid, threads, smem, stream>>>(res, nullptr, w, (T*)y, nullptr, part, groups, eps);
+    }
+    return tb_launch_status();
+}
+
+}  // namespace
+
+// res: 32-bit [rows, width]; upd: null or [rows, width] of upd_dtype; y: [rows, width] of y_dtype; res_out (32-bit,
+// may alias res) is written only when upd is given.
+TB_EXPORT int tb_group_rms_norm(const float* res, const void* upd, int upd_dtype, const float* w, void* y, int y_dtype,
+                                float* res_out, int rows, int width, int groups, float eps, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (groups < 1 || width < groups || width % groups != 0) return TB_ERR_BAD_SIZE;
+    if (upd != nullptr && res_out == nullptr) return TB_ERR_BAD_SIZE;
+    const bool uf = upd == nullptr || upd_dtype == TB_F32;
+    if (!uf && upd_dtype != TB_BF16) return TB_ERR_BAD_DTYPE;
+    if (y_dtype == TB_F32)
+        return uf ? launch_group<float, float>(res, upd, w, y, res_out, rows, width, groups, eps, stream)
+                  : launch_group<__nv_bfloat16, float>(res, upd, w, y, res_out, rows, width, groups, eps, stream);
+    if (y_dtype == TB_BF16)
+        return uf ? launch_group<float, __nv_bfloat16>(res, upd, w, y, res_out, rows, width, groups, eps, stream)
+                  : launch_group<__nv_bfloat16, __nv_bfloat16>(res, upd, w, y, res_out, rows, width, groups, eps, stream);
     return TB_ERR_BAD_DTYPE;
 }

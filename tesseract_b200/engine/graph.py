@@ -40,7 +40,7 @@ def graph_safe(model) -> bool:
     of the step context."""
     parts = [model.embedding, model.final_norm, model.head]
     for block in model.layers:
-        parts += [block.mixer, block.feed_forward, *block.norms.values()]
+        parts += [block.mixer, *block.norms.values()] + ([block.feed_forward] if block.feed_forward is not None else [])
     return all(getattr(part, "graph_safe", False) for part in parts)
 
 

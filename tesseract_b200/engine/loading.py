@@ -42,8 +42,12 @@ def load_model(model_dir: str, dtype: str = "bfloat16", device_index: int = 0) -
     from .. import kernels
 
     device = require_cuda(device_index)
-    kernels.prepare(parse_dtype(dtype))
     architecture, config, spec = load_model_description(model_dir)
+    run_dtype = parse_dtype(dtype)
+    libraries = None
+    if architecture.kernel_libraries is not None:
+        libraries = list(architecture.kernel_libraries(config, "float32" if run_dtype == torch.float32 else "bfloat16"))
+    kernels.prepare(run_dtype, libraries)
     tensors = check_and_load(model_dir, expected_tensors(spec), architecture.ignorable_tensors(config))
     return DecoderModel(spec, tensors, Runtime(parse_dtype(dtype), device))
 

@@ -49,12 +49,13 @@ _LIBRARIES = {
 }
 
 
-def prepare(dtype: torch.dtype) -> None:
+def prepare(dtype: torch.dtype, libraries=None) -> None:
     """Build, side by side, the kernel libraries that a model of this dtype uses (they would otherwise be built
-    one after the other, each at its first call)."""
+    one after the other, each at its first call).  ``libraries``: the model's own list (an architecture may name
+    the kernel files its parts call, so that a first call compiles those and no others)."""
     from .csrc.build import ensure_built
 
-    ensure_built(_LIBRARIES.get(dtype, ()))
+    ensure_built(libraries if libraries is not None else _LIBRARIES.get(dtype, ()))
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -713,4 +714,141 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, r
                                     _ptr(part_ml), _i64(part_ml.numel() if part_ml is not None else 0),
                                     _ptr(counters), _i64(counters.numel() if counters is not None else 0),
                                     _ptr(_error_word(q.device)), _stream()), "attention_tcgen05")
+    return out
+
+
+# ----------------------------------------------------------------------------- parts with a 32-bit residual stream
+
+
+def embedding_widen(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[t] = float32(table[tokens[t]])`` for a bfloat16 table and a float32 ``out``."""
+    _cuda(tokens, table, out)
+    _need(tokens.dtype == torch.int32 and tokens.is_contiguous(), "tokens must be contiguous int32")
+    _need(table.dtype == torch.bfloat16 and out.dtype == torch.float32 and table.is_contiguous()
+          and out.is_contiguous(), "embedding_widen takes a bfloat16 table and a float32 out")
+    rows, hidden = out.shape
+    _need(tokens.numel() == rows and table.shape[1] == hidden, "embedding shapes disagree")
+    lib = load_library("elementwise")
+    _check(lib.tb_embedding_widen(_ptr(tokens), _ptr(table), _ptr(out), _i32(rows), _i32(hidden),
+                                  _i32(table.shape[0]), _stream()), "embedding_widen")
+    return out
+
+
+def group_rms_norm(residual: torch.Tensor, update: Optional[torch.Tensor], weight: torch.Tensor, groups: int,
+                   eps: float, out: torch.Tensor) -> torch.Tensor:
+    """RMS norm over ``groups`` equal consecutive parts of each row of a float32 residual stream.  With ``update``
+    the sum ``residual + update`` is stored back into ``residual`` (32-bit) and normalised; ``out`` (float32 or
+    bfloat16) receives ``part / sqrt(mean(part^2) + eps) * weight``."""
+    _cuda(residual, update, weight, out)
+    rows, width = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "group_rms_norm: the stream is contiguous float32")
+    _need(out.shape == residual.shape and out.is_contiguous(), "group_rms_norm out")
+    _need(weight.dtype == torch.float32 and weight.numel() == width and weight.is_contiguous(),
+          "group_rms_norm weight must be a contiguous float32 vector of the row width")
+    if update is not None:
+        _need(update.shape == residual.shape and update.is_contiguous(), "group_rms_norm update")
+    lib = load_library("norm")
+    _check(lib.tb_group_rms_norm(_ptr(residual), _ptr(update), _i32(_code(update.dtype) if update is not None else 0),
+                                 _ptr(weight), _ptr(out), _i32(_code(out.dtype)), _ptr(residual), _i32(rows),
+                                 _i32(width), _i32(groups), _f32(eps), _stream()), "group_rms_norm")
+    return out
+
+
+def polynorm(z: torch.Tensor, coefficients: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """``out = a N(z) + b N(z^2) + c N(z^3) + e`` per row, ``N`` the division by the row's root mean square;
+    ``coefficients`` is float32 ``[4]`` on the device."""
+    _cuda(z, coefficients, out)
+    rows, width = z.shape
+    _need(z.stride(1) == 1 and out.stride(1) == 1 and out.shape == z.shape and out.dtype == z.dtype, "polynorm z/out")
+    _need(coefficients.dtype == torch.float32 and coefficients.numel() == 4 and coefficients.is_contiguous(),
+          "polynorm takes four float32 coefficients")
+    lib = load_library("polynorm")
+    _check(lib.tb_polynorm(_ptr(z), _i64(z.stride(0)), _ptr(coefficients), _ptr(out), _i64(out.stride(0)), _i32(rows),
+                           _i32(width), _f32(eps), _i32(_code(z.dtype)), _stream()), "polynorm")
+    return out
+
+
+def conv_rope_cache(proj: torch.Tensor, taps: torch.Tensor, state: Optional[torch.Tensor], q_out: torch.Tensor,
+                    cache: torch.Tensor, positions: torch.Tensor, seq_of_row: torch.Tensor, row_start: torch.Tensor,
+                    seq_begin: torch.Tensor, state_slots: torch.Tensor, block_table: torch.Tensor,
+                    inv_freq: Optional[torch.Tensor], *, num_seqs: int, heads: int, kv_heads: int, dim: int, vdim: int,
+                    rot_dims: int, page_size: int, write_kv: bool, single: bool) -> None:
+    """Short causal convolutions over the q, k and v channels of ``proj`` (``taps`` float32 ``[channels, J]``,
+    ``state`` float32 ``[slots, J - 1, channels]``), pairwise rotation of the first ``rot_dims`` numbers of every
+    query and key head, queries into ``q_out``, keys and values into the pages of ``cache``.  ``single``: every
+    sequence brings one row (the state is renewed inside the kernel); otherwise a second launch renews it."""
+    _cuda(proj, taps, state, q_out, cache, positions, seq_of_row, row_start, seq_begin, state_slots, block_table, inv_freq)
+    rows = q_out.shape[0]
+    channels = heads * dim + kv_heads * (dim + vdim)
+    count = taps.shape[1]
+    _need(proj.stride(1) == 1 and proj.shape[1] >= channels and proj.shape[0] == rows, "conv_rope_cache proj")
+    _need(q_out.stride(1) == 1 and q_out.shape[1] == heads * dim and q_out.dtype == proj.dtype, "conv_rope_cache q_out")
+    _need(cache.dtype == proj.dtype and cache.is_contiguous(), "conv_rope_cache cache dtype")
+    _need(taps.dtype == torch.float32 and taps.is_contiguous() and taps.shape[0] == channels, "conv_rope_cache taps")
+    if count > 1:
+        _need(state is not None and state.dtype == torch.float32 and state.is_contiguous()
+              and tuple(state.shape[1:]) == (count - 1, channels), "conv_rope_cache state")
+    if rot_dims:
+        _need(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2,
+              "conv_rope_cache inv_freq")
+    for t in (positions, seq_of_row, row_start, seq_begin, state_slots, block_table):
+        _need(t.dtype == torch.int32, "conv_rope_cache metadata must be int32")
+    lib = load_library("conv_rope_cache")
+    _check(lib.tb_conv_rope_cache(_ptr(proj), _i64(proj.stride(0)), _ptr(taps), _ptr(state), _ptr(q_out),
+                                  _i64(q_out.stride(0)), _ptr(cache), _ptr(positions), _ptr(seq_of_row), _ptr(row_start),
+                                  _ptr(seq_begin), _ptr(state_slots), _ptr(block_table), _i32(block_table.stride(0)),
+                                  _ptr(inv_freq), _i32(rows), _i32(heads), _i32(kv_heads), _i32(dim), _i32(vdim),
+                                  _i32(rot_dims), _i32(count), _i32(page_size), _i32(1 if write_kv else 0),
+                                  _i32(1 if single else 0), _i32(_code(proj.dtype)), _stream()), "conv_rope_cache")
+    if not single and count > 1:
+        _check(lib.tb_conv_state_update(_ptr(proj), _i64(proj.stride(0)), _ptr(state), _ptr(row_start), _ptr(seq_begin),
+                                        _ptr(state_slots), _i32(num_seqs), _i32(channels), _i32(count),
+                                        _i32(_code(proj.dtype)), _stream()), "conv_state_update")
+
+
+MASK_CAUSAL, MASK_WINDOW, MASK_BLOCKS = 0, 1, 2
+
+
+def attention_masked(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, cache: torch.Tensor,
+                     positions: torch.Tensor, seq_of_row: torch.Tensor, block_table: torch.Tensor, *, heads: int,
+                     kv_heads: int, dim: int, vdim: int, page_size: int, mask_kind: int, mask_size: int, sink: bool,
+                     scale: float) -> torch.Tensor:
+    """Paged attention with 32-bit scores and weights: ``q`` ``[T, heads * dim]``, optional ``gate``
+    ``[T, heads * vdim]`` (the output is multiplied by its sigmoid), ``out`` ``[T, heads * vdim]``; pages hold
+    ``[kv_heads, page_size, dim]`` keys then ``[kv_heads, page_size, vdim]`` values.  ``mask_kind``: causal, window
+    or blocks of ``mask_size`` positions; ``sink``: one more entry of score 0 in the softmax's denominator."""
+    _cuda(q, gate, out, cache, positions, seq_of_row, block_table)
+    rows = q.shape[0]
+    _need(q.stride(1) == 1 and q.shape[1] == heads * dim, "attention_masked q")
+    _need(out.stride(1) == 1 and out.shape == (rows, heads * vdim) and out.dtype == q.dtype, "attention_masked out")
+    _need(cache.dtype == q.dtype and cache.is_contiguous(), "attention_masked cache")
+    if gate is not None:
+        _need(gate.stride(1) == 1 and gate.shape == (rows, heads * vdim) and gate.dtype == q.dtype, "attention_masked gate")
+    lib = load_library("attention_masked")
+    _check(lib.tb_attention_masked(_ptr(q), _i64(q.stride(0)), _ptr(gate), _i64(gate.stride(0) if gate is not None else 0),
+                                   _ptr(out), _i64(out.stride(0)), _ptr(cache), _ptr(positions), _ptr(seq_of_row),
+                                   _ptr(block_table), _i32(block_table.stride(0)), _i32(rows), _i32(heads),
+                                   _i32(kv_heads), _i32(dim), _i32(vdim), _i32(page_size), _i32(mask_kind),
+                                   _i32(mask_size), _i32(1 if sink else 0), _f32(scale), _i32(_code(q.dtype)),
+                                   _stream()), "attention_masked")
+    return out
+
+
+def gated_recurrence(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor,
+                     out: torch.Tensor, row_start: torch.Tensor, state_slots: torch.Tensor, *, num_seqs: int,
+                     max_new: int) -> torch.Tensor:
+    """The minGRU recurrence with its output gate over ``proj`` ``[T, 3 * width]`` (update gate | candidate | output
+    gate, before biases and activations); ``state`` float32 ``[slots, width]`` is read and renewed per sequence."""
+    _cuda(proj, bias_z, bias_x, state, out, row_start, state_slots)
+    rows, width = out.shape
+    _need(proj.stride(1) == 1 and proj.shape == (rows, 3 * width), "gated_recurrence proj")
+    _need(out.stride(1) == 1, "gated_recurrence out")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == width, "gated_recurrence state")
+    for b in (bias_z, bias_x):
+        _need(b.dtype == torch.float32 and b.numel() == width and b.is_contiguous(), "gated_recurrence bias")
+    lib = load_library("gated_recurrence")
+    _check(lib.tb_gated_recurrence(_ptr(proj), _i64(proj.stride(0)), _i32(_code(proj.dtype)), _ptr(bias_z), _ptr(bias_x),
+                                   _ptr(state), _ptr(out), _i64(out.stride(0)), _i32(_code(out.dtype)), _ptr(row_start),
+                                   _ptr(state_slots), _i32(num_seqs), _i32(width), _i32(max_new), _stream()),
+           "gated_recurrence")
     return out

@@ -27,13 +27,14 @@ def _part_specs(spec: ModelSpec):
     for layer in spec.layers:
         block_cls = BLOCKS.get(layer.block)
         norms = layer.norms
-        for role in block_cls.norm_roles():
+        for role in block_cls.norm_roles(with_feed_forward=layer.feed_forward is not None):
             if role not in norms:
                 raise ValueError(f"block '{layer.block}' needs a norm for role '{role}'")
         for role in sorted(norms):
             yield NORMS, norms[role]
         yield MIXERS, layer.mixer
-        yield FEED_FORWARDS, layer.feed_forward
+        if layer.feed_forward is not None:
+            yield FEED_FORWARDS, layer.feed_forward
     yield NORMS, spec.final_norm
     yield HEADS, spec.head
 
@@ -79,7 +80,7 @@ class DecoderModel:
             block_cls = BLOCKS.get(layer.block)
             norms = {role: build(NORMS, part) for role, part in layer.norms.items()}
             mixer = build(MIXERS, layer.mixer)
-            feed_forward = build(FEED_FORWARDS, layer.feed_forward)
+            feed_forward = build(FEED_FORWARDS, layer.feed_forward) if layer.feed_forward is not None else None
             self.layers.append(block_cls(norms, mixer, feed_forward))
         self.final_norm = build(NORMS, spec.final_norm)
         # A head that names the embedding's checkpoint tensor (tied embeddings) gets the same host tensor, and the

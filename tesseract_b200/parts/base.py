@@ -14,9 +14,10 @@ Kinds and what each must provide:
     views in place; optionally ``rotary_inv_freq`` (a float32 ``[head_dim/2]`` device tensor)
     with which an attention mixer may fuse rotation into its cache write.
 ``Mixer``
-    ``cache_need()`` -> ``None`` | :class:`PagedKVNeed` | :class:`StateNeed`;
-    ``forward(x, ctx, cache)`` -> ``[T, hidden]``.  ``ctx`` is the step's
-    :class:`StepContext`; ``cache`` the :class:`CacheBinding` of this run entry.
+    ``cache_need()`` -> ``None`` | a :class:`PagedNeed` | :class:`StateNeed` | a tuple of these (a mixer that
+    keeps pages and fixed-size state, say); ``forward(x, ctx, cache)`` -> ``[T, hidden]``.  ``ctx`` is the step's
+    :class:`StepContext`; ``cache`` the :class:`CacheBinding` of this run entry (a tuple of bindings, in the
+    order of the needs, for a tuple of needs).
 ``FeedForward``
     ``forward(x, ctx)`` -> ``[T, hidden]``.
 ``Block``
@@ -127,6 +128,19 @@ class PagedNeed:
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
         raise NotImplementedError
 
+    def first_needed_position(self, next_position: int) -> int:
+        """The lowest position that a query at ``next_position`` or later can still read: pages wholly below it go
+        back to the pool.  A subclass with another rule of forgetting (blocks of positions, say) overrides this and
+        :meth:`live_span`."""
+        if self.window:
+            return max(0, next_position - self.window + 1)
+        return 0
+
+    def live_span(self) -> Optional[int]:
+        """The most positions below a query's own that it can read (None: all of them); with the rows of a step it
+        bounds the pages a request holds at any one time."""
+        return self.window - 1 if self.window else None
+
 
 @dataclass(frozen=True)
 class PagedKVNeed(PagedNeed):
@@ -139,6 +153,35 @@ class PagedKVNeed(PagedNeed):
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
         return (2, self.num_kv_heads, page_size, self.head_dim)
+
+
+@dataclass(frozen=True)
+class PagedKeyValueNeed(PagedNeed):
+    """Keys of ``key_dim`` and values of ``value_dim`` numbers per kv head: a page is one run of
+    ``kv_heads * page_size * key_dim`` keys (``[kv_heads, page_size, key_dim]``) followed by
+    ``[kv_heads, page_size, value_dim]`` values.  ``window``: only the last ``window`` tokens are read.  ``block``: the
+    positions are cut into consecutive blocks of that many, counted from 0, and a query reads only its own block, so
+    the pages of earlier blocks go back to the pool."""
+
+    num_kv_heads: int = 1
+    key_dim: int = 0
+    value_dim: int = 0
+    window: Optional[int] = None
+    block: Optional[int] = None
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        return (self.num_kv_heads * page_size * (self.key_dim + self.value_dim),)
+
+    def first_needed_position(self, next_position: int) -> int:
+        first = PagedNeed.first_needed_position(self, next_position)
+        if self.block:
+            first = max(first, (next_position // self.block) * self.block)
+        return first
+
+    def live_span(self) -> Optional[int]:
+        spans = [s for s in (self.window - 1 if self.window else None, self.block - 1 if self.block else None)
+                 if s is not None]
+        return min(spans) if spans else None
 
 
 @dataclass(frozen=True)
@@ -357,7 +400,7 @@ class Block:
     # return a stream whose ``prepared`` is set for it.
     accepts_next_norm = False
 
-    def __init__(self, norms: Mapping[str, Norm], mixer: Mixer, feed_forward: FeedForward):
+    def __init__(self, norms: Mapping[str, Norm], mixer: Mixer, feed_forward: Optional[FeedForward]):
         self.norms = dict(norms)
         self.mixer = mixer
         self.feed_forward = feed_forward
@@ -367,7 +410,8 @@ class Block:
         return None
 
     @classmethod
-    def norm_roles(cls) -> Tuple[str, ...]:
+    def norm_roles(cls, with_feed_forward: bool = True) -> Tuple[str, ...]:
+        """The norms the arrangement needs; a layer whose feed-forward is None asks with ``with_feed_forward`` False."""
         return ()
 
     def forward(self, stream: ResidualStream, ctx: StepContext, cache: Optional[CacheBinding]) -> ResidualStream:

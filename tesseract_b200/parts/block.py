@@ -7,6 +7,9 @@
     m  = post_mixer_norm(residual + a)
     f  = feed_forward(m)            -> leaves (residual, f) for the next block's norm
 
+A layer without a feed-forward (``feed_forward`` None) ends after the mixer: ``(residual, a)`` goes to the next
+block's norm, and the role ``post_mixer`` needs no norm.
+
 Each addition is fused into the norm that follows it; where the part in front can, its last product does that
 norm's work on the way out (``FollowNorm`` -> ``PreparedNorm``), and the product behind only applies the scale.
 """
@@ -22,8 +25,8 @@ from .base import (BLOCKS, Block, CacheBinding, DeferredNorm, FollowNorm, Norm, 
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
     @classmethod
-    def norm_roles(cls) -> Tuple[str, ...]:
-        return ("input", "post_mixer")
+    def norm_roles(cls, with_feed_forward: bool = True) -> Tuple[str, ...]:
+        return ("input", "post_mixer") if with_feed_forward else ("input",)
 
     accepts_next_norm = True
 
@@ -38,6 +41,8 @@ class PreNormBlock(Block):
         else:
             first = DeferredNorm(self.norms["input"], stream.residual, stream.update)
         x = first if self.mixer.accepts_deferred_norm else first.materialize()
+        if self.feed_forward is None:
+            return ResidualStream(first.residual, self.mixer.forward(x, ctx, cache))
         if self.mixer.accepts_follow_norm:
             mixed = self.mixer.forward(x, ctx, cache, follow=FollowNorm(self.norms["post_mixer"], first))
         else:

@@ -20,7 +20,8 @@ from .linear import BestOfRows, Linear
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
-    """params: ``vocab_size, hidden_size``; weights: ``table``."""
+    """params: ``vocab_size, hidden_size``, optional ``stream`` (``"float32"``: the rows come out in 32-bit whatever
+    the run dtype, for a model whose residual stream is kept in 32-bit); weights: ``table``."""
 
     graph_safe = True
 
@@ -29,6 +30,10 @@ class TokenEmbedding(Embedding):
         self.vocab_size = int(spec.params["vocab_size"])
         self.hidden_size = int(spec.params["hidden_size"])
         self.table = runtime.matrix(tensors["table"])
+        stream = spec.params.get("stream")
+        if stream not in (None, "float32"):
+            raise ValueError(f"an embedding's stream is the run dtype or 'float32', got '{stream}'")
+        self.widen = stream == "float32" and self.table.dtype != torch.float32
 
     @classmethod
     def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
@@ -36,6 +41,10 @@ class TokenEmbedding(Embedding):
         return {spec.weights["table"]: ExpectedTensor((int(p["vocab_size"]), int(p["hidden_size"])))}
 
     def forward(self, token_ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.widen:
+            if out is None:
+                out = torch.empty((token_ids.numel(), self.hidden_size), dtype=torch.float32, device=self.table.device)
+            return kernels.embedding_widen(token_ids, self.table, out)
         if out is None:
             out = torch.empty((token_ids.numel(), self.hidden_size), dtype=self.table.dtype, device=self.table.device)
         return kernels.embedding(token_ids, self.table, out)

@@ -71,3 +71,47 @@ class SwiGLU(FeedForward):
             activated = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
             kernels.silu_mul(gate_up, activated, interleaved=self.interleaved)
         return self.down_proj.forward(activated, follow=follow)
+
+
+@FEED_FORWARDS.register("polynorm_mlp")
+class PolyNormMLP(FeedForward):
+    """A dense feed-forward ``down(act(up h))`` whose activation is a normalised polynomial:
+
+        act(z) = a N(z) + b N(z^2) + c N(z^3) + e,      N(v) = v / sqrt(mean(v^2) + eps) over the row,
+
+    with powers taken element by element and ``(a, b, c, e)`` a tensor of four numbers.  params: ``hidden_size,
+    intermediate_size, eps``, optional ``stream``; weights: ``up, down, act``.  The activation is one kernel with
+    32-bit statistics; the down product comes out in 32-bit for a residual stream kept in 32-bit."""
+
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        super().__init__(spec, tensors, runtime)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.intermediate_size = int(p["intermediate_size"])
+        self.eps = float(p["eps"])
+        self.stream_f32 = p.get("stream") == "float32"
+        self.up_proj = Linear(tensors["up"], runtime)
+        self.down_proj = Linear(tensors["down"], runtime)
+        self.coefficients = runtime.vector_f32(tensors["act"])
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
+        p, w = spec.params, spec.weights
+        hidden, inter = int(p["hidden_size"]), int(p["intermediate_size"])
+        return {w["up"]: ExpectedTensor((inter, hidden)), w["down"]: ExpectedTensor((hidden, inter)),
+                w["act"]: ExpectedTensor((4,))}
+
+    @classmethod
+    def random_tensor(cls, spec, role, shape, generator) -> torch.Tensor:
+        if role == "act":
+            return torch.tensor([0.6, 0.3, 0.2, 0.05]) + torch.randn(shape, generator=generator) * 0.05
+        return torch.randn(shape, generator=generator, dtype=torch.float32) * (shape[-1] ** -0.5)
+
+    def forward(self, x, ctx: StepContext, follow=None):
+        if isinstance(x, DeferredNorm):
+            x = x.materialize()
+        z = self.up_proj.forward(x)
+        kernels.polynorm(z, self.coefficients, self.eps, z)        # in place: a row is read whole before it is written
+        return self.down_proj.forward(z, float32_out=self.stream_f32)

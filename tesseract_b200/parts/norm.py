@@ -54,3 +54,43 @@ class RMSNorm(Norm):
             out = torch.empty_like(residual)
         kernels.add_rms_norm(residual, update, self.weight, self.eps, out, residual)
         return out
+
+
+@NORMS.register("grouped_rms_norm")
+class GroupedRMSNorm(Norm):
+    """RMS norm over equal consecutive parts of the vector, for a residual stream kept in 32-bit.
+
+    params: ``size``, ``groups``, ``eps``; weights: ``weight`` ``[size]``.  The row is cut into ``groups`` parts, each
+    is divided by its own ``sqrt(mean(part^2) + eps)``, and the whole is multiplied by ``weight``; ``groups = 1`` is
+    the plain norm.  The stream (``x`` / ``residual``) is float32 whatever the run dtype, an update may be float32
+    or bfloat16, and the normalised rows come out in the run dtype, rounded once."""
+
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        super().__init__(spec, tensors, runtime)
+        params = spec.params
+        self.size = int(params["size"])
+        self.groups = int(params.get("groups") or 1)
+        self.eps = float(params["eps"])
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"a norm over {self.groups} groups needs a size that they divide, got {self.size}")
+        self.weight = runtime.vector_f32(tensors["weight"])
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
+        return {spec.weights["weight"]: ExpectedTensor((int(spec.params["size"]),))}
+
+    @classmethod
+    def random_tensor(cls, spec, role, shape: Tuple[int, ...], generator) -> torch.Tensor:
+        return 1.0 + torch.randn(shape, generator=generator, dtype=torch.float32) * 0.1
+
+    def _out(self, x: torch.Tensor, out: Optional[torch.Tensor]) -> torch.Tensor:
+        return out if out is not None else torch.empty(x.shape, dtype=self.runtime.dtype, device=x.device)
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return kernels.group_rms_norm(x, None, self.weight, self.groups, self.eps, self._out(x, out))
+
+    def forward_add(self, residual: torch.Tensor, update: torch.Tensor,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return kernels.group_rms_norm(residual, update, self.weight, self.groups, self.eps, self._out(residual, out))

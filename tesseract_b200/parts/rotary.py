@@ -67,6 +67,33 @@ class RotaryEncoding(PositionEncoding):
         raise NotImplementedError("rotary encoding is applied by the attention mixer's fused rotate-and-store kernel")
 
 
+@POSITION_ENCODINGS.register("rotary_pairs")
+class RotaryPairs(PositionEncoding):
+    """Rotation of neighbouring pairs: of every head's first ``dims`` numbers, numbers ``2i`` and ``2i + 1`` turn by
+    ``position * base^(-2i / dims)``; the rest of the head passes unchanged.
+
+    params: ``head_dim``, ``dims`` (even, at most ``head_dim``), ``base``.  The frequencies are taken in 64-bit on
+    the host and rounded once to 32-bit; the angle and its sine and cosine are 32-bit, in the kernel that applies
+    them (the mixer's convolve-rotate-and-store kernel reads ``pair_inv_freq`` and ``dims``)."""
+
+    def __init__(self, spec: PartSpec, tensors, runtime: Runtime):
+        super().__init__(spec, tensors, runtime)
+        params = spec.params
+        self.head_dim = int(params["head_dim"])
+        self.dims = int(params["dims"])
+        self.base = float(params["base"])
+        if self.dims < 0 or self.dims % 2 or self.dims > self.head_dim:
+            raise ValueError(f"rotation over pairs needs an even number of dimensions up to {self.head_dim}, got {self.dims}")
+        if not self.base > 0.0:
+            raise ValueError("the rotation's base must be positive")
+        self.inv_freq_host = np.asarray([self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)],
+                                        dtype=np.float64).astype(np.float32)
+        self.pair_inv_freq = torch.from_numpy(self.inv_freq_host).to(runtime.device) if self.dims else None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        raise NotImplementedError("the pair rotation is applied by the mixer's convolve-rotate-and-store kernel")
+
+
 @POSITION_ENCODINGS.register("none")
 class NoPositionEncoding(PositionEncoding):
     """Leaves queries and keys as they are."""

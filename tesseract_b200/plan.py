@@ -249,7 +249,8 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
                         f"(context {context}, pages of {page_size})"]
     seen = {}
     for index, block in enumerate(model.layers):
-        key = (repr(model.spec.layers[index].mixer.params), repr(model.spec.layers[index].feed_forward.params))
+        ff_spec = model.spec.layers[index].feed_forward
+        key = (repr(model.spec.layers[index].mixer.params), repr(ff_spec.params if ff_spec is not None else None))
         if key in seen:
             seen[key].append(index)
             continue
@@ -257,7 +258,7 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
     for key, layers in seen.items():
         block = model.layers[layers[0]]
         lines.append(f"layers {layers[0]}..{layers[-1]} ({len(layers)}): mixer '{block.mixer.kind}', "
-                     f"feed-forward '{block.feed_forward.kind}'")
+                     f"feed-forward '{block.feed_forward.kind if block.feed_forward is not None else None}'")
         for rows in row_counts:
             lines.append(f"  {rows} rows")
             mixer, ffn = block.mixer, block.feed_forward
@@ -291,7 +292,7 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
                 prepared = isinstance(mixer, Attention) and o_plan.prepares_norm
                 lines.append(f"    gate/up  {product(dtype, rows, gu.out_features, gu.in_features, epilogue=epilogue, norm='prepared' if prepared else 'add_norm')}")
                 lines.append(f"    down     {product(dtype, rows, down.out_features, down.in_features, follow=True)}")
-            else:
+            elif ffn is not None:
                 lines.append(f"    feed-forward '{ffn.kind}' (its own code)")
     proj = getattr(model.head, "proj", None)
     if proj is not None:
