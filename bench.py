@@ -662,6 +662,239 @@ def run_kernels(args):
     return 0
 
 
+
+# ----------------------------------------------------------------------------- another design beside Llama
+# `--design revesun`: prefill and decode of a Revesun model at layer sizes like a real model's (random weights),
+# beside a Llama of the same width, heads, head sizes, layer count and about as many weights a layer, measured the
+# same way; then the design's own kernels alone, against the bytes they must move.  The default workload is untouched.
+DESIGN_SIZES = {
+    "1b": dict(width=2048, heads=32, kv_heads=8, dim=64, layers=16, llama_ff=8192, dense_ff=12288, block=128, taps=4,
+               rot_dims=32, groups=2),
+    "3b": dict(width=3072, heads=24, kv_heads=8, dim=128, layers=12, llama_ff=8192, dense_ff=12288, block=256, taps=4,
+               rot_dims=64, groups=2),
+    "8b": dict(width=4096, heads=32, kv_heads=8, dim=128, layers=8, llama_ff=14336, dense_ff=21504, block=256, taps=4,
+               rot_dims=64, groups=4),
+}
+DESIGN_VOCAB = 32768
+
+
+def revesun_config(size, layers):
+    z = DESIGN_SIZES[size]
+    attention = {"type": "attention",
+                 "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                           "conv": z["taps"], "mask": {"size": z["block"]},
+                           "rot": {"dims": z["rot_dims"], "base": 10000.0}, "scale": z["dim"] ** -0.5},
+                 "mlp": {"kind": "dense", "ff": z["dense_ff"]}}
+    recurrent = {"type": "mingru", "mixer": {"width": z["width"]}, "mlp": None}
+    return {"architecture": "Revesun", "torch_dtype": "bfloat16", "width": z["width"], "vocab": DESIGN_VOCAB,
+            "norm": {"eps": 1e-5, "groups": z["groups"]},
+            "layers": [recurrent if i % 4 == 3 else attention for i in range(layers)]}
+
+
+def run_design(args):
+    import numpy as np
+    import torch
+
+    from tesseract_b200 import LLM, kernels
+    from tesseract_b200.engine import StepEntry
+    from tesseract_b200.weights.random_init import write_random_model
+
+    z = DESIGN_SIZES[args.size]
+    layers = args.layers or z["layers"]
+    pk = peaks()
+    rng = np.random.default_rng(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")      # larger than L2: written between timed steps
+    llama = dict(LLAMA_1B, num_hidden_layers=layers, hidden_size=z["width"], num_attention_heads=z["heads"],
+                 num_key_value_heads=z["kv_heads"], head_dim=z["dim"], intermediate_size=z["llama_ff"],
+                 vocab_size=DESIGN_VOCAB, bos_token_id=1, eos_token_id=[2])
+    batches = (8, 64)
+    steps, warmup = min(args.steps, 64), max(3, min(args.warmup, 8))
+    sampler = ClockSampler()
+    windows = []
+    sampler.start()
+
+    def measure(config):
+        scratch = tempfile.TemporaryDirectory(prefix="tesseract_bench_")
+        write_random_model(scratch.name, config, seed=0)
+        vocab = config.get("vocab") or config["vocab_size"]
+        capacity = max(batches) * (PROMPT_TOKENS + steps + warmup + 64)
+        llm = LLM(scratch.name, dtype="bfloat16", max_running=max(batches), max_batch_tokens=4096,
+                  prefill_chunk_tokens=PROMPT_TOKENS, kv_capacity_tokens=capacity, page_size=PAGE_SIZE,
+                  max_sequence_length=CONTEXT, cuda_graphs=not args.no_graphs)
+        stepper, cache = llm.stepper, llm.stepper.cache
+        out = {"weights_gb": os.path.getsize(os.path.join(scratch.name, "model.safetensors")) / 1e9}
+        times = []
+        for k in range(3 + 10):                        # one 2,048-token prompt in one step; three warm-ups
+            assert cache.admit("p")
+            tokens = rng.integers(0, vocab, PROMPT_TOKENS).tolist()
+            flush.fill_(k)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0 = time.time()
+            start.record()
+            stepper.step([StepEntry("p", tokens, [PROMPT_TOKENS - 1])])
+            stop.record()
+            torch.cuda.synchronize()
+            windows.append((t0, time.time()))
+            cache.release("p")
+            if k >= 3:
+                times.append(start.elapsed_time(stop))
+        ms = statistics.median(times)
+        out["prefill"] = {"tokens": PROMPT_TOKENS, "ms": ms, "tokens_per_s": PROMPT_TOKENS / (ms / 1e3),
+                          "fastest_ms": min(times), "slowest_ms": max(times)}
+        out["decode"] = {}
+        for batch in batches:
+            ids = [f"d{batch}_{k}" for k in range(batch)]
+            for rid in ids:
+                assert cache.admit(rid)
+                stepper.step([StepEntry(rid, rng.integers(0, vocab, PROMPT_TOKENS).tolist(), [])])
+            greedy, ones = [0.0] * batch, [1.0] * batch
+            last = [int(t) for t in rng.integers(0, vocab, batch)]
+            for _ in range(warmup):
+                last = stepper.step_and_sample([StepEntry(r, [t], [0]) for r, t in zip(ids, last)], greedy, ones, greedy)
+            before = kernels.launch_count + (stepper.graphs.kernels_replayed if stepper.graphs else 0)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0 = time.time()
+            start.record()
+            for _ in range(steps):                     # the weights of a step (more than L2 at these sizes) are the flush
+                last = stepper.step_and_sample([StepEntry(r, [t], [0]) for r, t in zip(ids, last)], greedy, ones, greedy)
+            stop.record()
+            torch.cuda.synchronize()
+            windows.append((t0, time.time()))
+            ms_step = start.elapsed_time(stop) / steps
+            launches = kernels.launch_count + (stepper.graphs.kernels_replayed if stepper.graphs else 0) - before
+            out["decode"][str(batch)] = {"ms_per_step": ms_step, "tokens_per_s": batch / (ms_step / 1e3),
+                                         "context": cache.length(ids[0]), "kernels_per_step": launches / steps}
+            for rid in ids:
+                cache.release(rid)
+        del llm, stepper, cache
+        torch.cuda.empty_cache()
+        scratch.cleanup()
+        return out
+
+    result = {"design": "Revesun", "size": args.size, "layers": layers, "vocab": DESIGN_VOCAB, "dtype": "bf16",
+              "data": "synthetic", "l2": "a 256 MB buffer is written between timed prefill steps; a decode step "
+                                         "reads its weights, which exceed L2",
+              "revesun": measure(revesun_config(args.size, layers)), "llama": measure(llama)}
+    result["kernels"] = design_kernels(args.size, pk)
+    result["clocks"] = sampler.stop(windows)
+    result["peaks"] = pk
+    print(json.dumps(result))
+    return 0
+
+
+def design_kernels(size, pk):
+    """The design's own kernels alone at this size: 2,048 prompt rows of one sequence, and 64 decoded rows at context
+    2,048; device time per launch as the median over eight buffer sets that are walked in turn (together larger than
+    L2), the bytes each must move, and that against the measured copy bandwidth."""
+    import torch
+
+    from tesseract_b200 import kernels
+
+    z = DESIGN_SIZES[size]
+    dev = "cuda"
+    H, G, d, W, F = z["heads"], z["kv_heads"], z["dim"], z["width"], z["dense_ff"]
+    taps, block, page = z["taps"], z["block"], PAGE_SIZE
+    channels = H * d + 2 * G * d
+    inv_freq = torch.tensor([10000.0 ** (-2.0 * i / z["rot_dims"]) for i in range(z["rot_dims"] // 2)], device=dev)
+    SETS = 8
+    out = {}
+
+    def timed(name, make, nbytes, flops=0):
+        runs = [make(k) for k in range(SETS)]
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for run in runs:
+                run()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()                 # one graph of the eight launches: no host time between them
+        with torch.cuda.graph(graph):
+            for run in runs:
+                run()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3 / SETS)
+        us = statistics.median(times)
+        line = {"us": round(us, 2), "mb": round(nbytes / 1e6, 2), "gbs": round(nbytes / us / 1e3, 1),
+                "frac_of_measured_hbm": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+        if flops:
+            line["tflops_fp32"] = round(flops / us / 1e6, 2)
+        out[name] = line
+
+    for label, rows, seqs, begin in (("prefill_2048", 2048, 1, 0), ("decode_64", 64, 64, 2047)):
+        new = rows // seqs
+        positions = (torch.arange(rows, dtype=torch.int32, device=dev) % new) + begin
+        seq_of_row = torch.arange(rows, dtype=torch.int32, device=dev) // new
+        row_start = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * new
+        seq_begin = torch.full((seqs,), begin, dtype=torch.int32, device=dev)
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        pages_per_seq = 2048 // page
+        table = (torch.arange(seqs * pages_per_seq, dtype=torch.int32, device=dev) + 1).view(seqs, pages_per_seq)
+        page_elems = G * page * 2 * d
+
+        def norm(k):
+            res = torch.randn(rows, W, device=dev)
+            upd = torch.randn(rows, W, device=dev)
+            w = torch.ones(W, device=dev)
+            y = torch.empty(rows, W, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.group_rms_norm(res, upd, w, z["groups"], 1e-5, y)
+
+        timed(f"group_rms_norm+add/{label}", norm, rows * W * (4 + 4 + 4 + 2))
+
+        def conv(k):
+            proj = torch.randn(rows, channels + H * d, device=dev).bfloat16()
+            w = torch.randn(taps, channels, device=dev)
+            state = torch.zeros(seqs + 1, taps - 1, channels, device=dev)
+            q = torch.empty(rows, H * d, dtype=torch.bfloat16, device=dev)
+            cache = torch.zeros(seqs * pages_per_seq + 1, page_elems, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.conv_rope_cache(proj, w, state, q, cache, positions, seq_of_row, row_start, seq_begin,
+                                                   slots, table, inv_freq, num_seqs=seqs, heads=H, kv_heads=G, dim=d,
+                                                   vdim=d, rot_dims=z["rot_dims"], page_size=page, write_kv=True,
+                                                   single=new == 1)
+
+        timed(f"conv_rope_cache/{label}", conv, rows * channels * 2 * 2 + (seqs * (taps - 1) * channels * 8 if new == 1 else 0))
+
+        def attend(k):
+            q = torch.randn(rows, H * d, device=dev).bfloat16()
+            gate = torch.randn(rows, H * d, device=dev).bfloat16()
+            o = torch.empty(rows, H * d, dtype=torch.bfloat16, device=dev)
+            cache = torch.randn(seqs * pages_per_seq + 1, page_elems, device=dev).bfloat16()
+            return lambda: kernels.attention_masked(q, gate, o, cache, positions, seq_of_row, table, heads=H, kv_heads=G,
+                                                    dim=d, vdim=d, page_size=page, mask_kind=kernels.MASK_BLOCKS,
+                                                    mask_size=block, sink=True, scale=d ** -0.5)
+
+        keys_seen = sum(int(p) % block + 1 for p in positions.tolist())
+        kv_read = (2048 if new > 1 else seqs * (begin % block + 1)) * G * 2 * d * 2
+        timed(f"attention_masked/{label}", attend, rows * H * d * 2 * 3 + kv_read, flops=keys_seen * H * 2 * d * 2)
+
+        def recur(k):
+            proj = torch.randn(rows, 3 * W, device=dev)
+            bz, bx = torch.zeros(W, device=dev), torch.zeros(W, device=dev)
+            state = torch.zeros(seqs + 1, W, device=dev)
+            y = torch.empty(rows, W, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.gated_recurrence(proj, bz, bx, state, y, row_start, slots, num_seqs=seqs, max_new=new)
+
+        timed(f"gated_recurrence/{label}", recur, rows * W * (12 + 2))
+
+        def act(k):
+            x = torch.randn(rows, F, device=dev).bfloat16()
+            c = torch.tensor([0.6, 0.3, 0.2, 0.1], device=dev)
+            return lambda: kernels.polynorm(x, c, 1e-5, x)
+
+        timed(f"polynorm/{label}", act, rows * F * 2 * 2)
+    return out
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -683,12 +916,17 @@ def main():
     parser.add_argument("--workload", choices=["3b", "8b"], default=None,
                         help="run another workload instead of the headline one: continuous batching at the 3B sizes, "
                              "or a 2,048-token portion beside 64 decode rows at the 8B sizes")
+    parser.add_argument("--design", choices=["revesun"], default=None,
+                        help="instead of the headline workload: prefill and decode of this design beside a Llama of "
+                             "equal layer sizes (--size), and the design's own kernels alone")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
         return 2
+    if args.design:
+        return run_design(args)
     if args.workload:
         return run_workload(args)
     if args.only == "kernels":

@@ -16,6 +16,14 @@
 //
 // With block or window masks a row reads at most `mask_size` keys, so the work is linear in the rows of a step and
 // the same kernel serves prompt portions and single decoded rows.
+//
+// Two kernels.  The packet kernel takes head sizes that are multiples of a 16-byte packet (8 bfloat16, 4 floats):
+// a warp takes one row and up to four query heads of one kv head together, so that a key or value packet is
+// loaded and widened once for all of them; a block is eight neighbouring rows of the same heads, which read all
+// but a few of the same keys and meet in L1.  Scores: a lane a key, the key's packets against the queries in
+// shared memory (read four numbers at a time).  Values: the warp is cut into groups of lanes that share a value
+// row, a lane a packet of columns, the weights passed through shared memory; the groups' partial sums meet at the
+// end in a fixed butterfly.  The element kernel takes every other size, a number at a time.
 #include "common.cuh"
 
 namespace {
@@ -115,6 +123,201 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
     }
 }
 
+
+constexpr int kRowsPerBlock = 8;      // warps of a block: neighbouring rows of the same heads
+
+// HPW: query heads of one kv head that a warp takes together (1, 2 or 4); NP: packets of value columns per lane;
+// lv: lanes that share a value row in the value phase (a power of two).
+template <typename T, int HPW, int NP>
+__global__ void __launch_bounds__(kRowsPerBlock * 32)
+attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict__ gate,
+                                int64_t gate_stride, T* __restrict__ out, int64_t out_stride,
+                                const T* __restrict__ cache, const int* __restrict__ positions,
+                                const int* __restrict__ seq_of_row, const int* __restrict__ block_table, int bt_stride,
+                                int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind,
+                                int mask_size, int sink, float scale, int lv) {
+    constexpr int N = Packet<T>::N;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kRowsPerBlock + warp;
+    const int head0 = blockIdx.y * HPW;
+    if (row >= rows) return;                          // the whole warp leaves; no block-wide barrier below
+    const size_t per_warp = 32 * sizeof(int64_t) + (size_t)HPW * (32 + dim) * sizeof(float);
+    int64_t* voffs = reinterpret_cast<int64_t*>(smem_raw + warp * per_warp);
+    float* ps = reinterpret_cast<float*>(voffs + 32);         // [HPW][32]
+    float* qs = ps + HPW * 32;                                // [HPW][dim]
+    const int kv_head = head0 / (heads / kv_heads);
+    const int pos = positions[row];
+    const int seq = seq_of_row[row];
+    int first_key = 0;
+    if (mask_kind == MASK_WINDOW) first_key = pos - mask_size + 1 > 0 ? pos - mask_size + 1 : 0;
+    else if (mask_kind == MASK_BLOCKS) first_key = (pos / mask_size) * mask_size;
+
+    const T* qrow = q + (int64_t)row * q_stride + (int64_t)head0 * dim;       // the HPW heads lie side by side
+    for (int i = lane * N; i < HPW * dim; i += 32 * N) Packet<T>::load(qrow + i, qs + i);
+    __syncwarp();
+
+    const int64_t page_elems = (int64_t)kv_heads * page_size * (dim + vdim);
+    const T* kbase = cache + (int64_t)kv_head * page_size * dim;
+    const T* vbase = cache + (int64_t)kv_heads * page_size * dim + (int64_t)kv_head * page_size * vdim;
+    const int* table = block_table + (int64_t)seq * bt_stride;
+    const int vg = lane / lv, vs = lane % lv;         // value phase: group vg owns keys vg, vg + 32 / lv, ...
+    const int value_step = 32 / lv;
+
+    float m[HPW], l[HPW], acc[HPW][NP][N];
+#pragma unroll
+    for (int h = 0; h < HPW; ++h) {
+        m[h] = sink ? 0.0f : -1.0e30f;
+        l[h] = sink ? 1.0f : 0.0f;
+#pragma unroll
+        for (int pk = 0; pk < NP; ++pk)
+#pragma unroll
+            for (int e = 0; e < N; ++e) acc[h][pk][e] = 0.0f;
+    }
+
+    for (int key0 = first_key; key0 <= pos; key0 += 32) {
+        const int key = key0 + lane;
+        const bool valid = key <= pos;
+        const int k = valid ? key : pos;              // (a lane behind the last key points at the last key)
+        const int64_t base = (int64_t)table[k / page_size] * page_elems;
+        const int in_page = k % page_size;
+        const T* kp = kbase + base + (int64_t)in_page * dim;
+        __syncwarp();                                 // the value phase of the block before has read voffs and ps
+        voffs[lane] = base + (int64_t)in_page * vdim;
+        // scores: a lane a key, the key's packets against the HPW queries in shared memory
+        float dot[HPW];
+#pragma unroll
+        for (int h = 0; h < HPW; ++h) dot[h] = 0.0f;
+#pragma unroll 2
+        for (int i = 0; i < dim; i += N) {
+            float kv[N];
+            Packet<T>::load(kp + i, kv);
+#pragma unroll
+            for (int h = 0; h < HPW; ++h) {
+#pragma unroll
+                for (int e = 0; e < N; e += 4) {
+                    const float4 qv = *reinterpret_cast<const float4*>(qs + h * dim + i + e);
+                    dot[h] = fmaf(qv.x, kv[e], dot[h]);
+                    dot[h] = fmaf(qv.y, kv[e + 1], dot[h]);
+                    dot[h] = fmaf(qv.z, kv[e + 2], dot[h]);
+                    dot[h] = fmaf(qv.w, kv[e + 3], dot[h]);
+                }
+            }
+        }
+        float corr[HPW];
+#pragma unroll
+        for (int h = 0; h < HPW; ++h) {
+            const float s = valid ? dot[h] * scale : -1.0e30f;
+            const float m_new = fmaxf(m[h], warp_max(s));
+            const float p = valid ? __expf(s - m_new) : 0.0f;
+            corr[h] = __expf(m[h] - m_new);
+            l[h] = l[h] * corr[h] + warp_sum(p);
+            m[h] = m_new;
+            ps[h * 32 + lane] = p;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int h = 0; h < HPW; ++h)
+#pragma unroll
+            for (int pk = 0; pk < NP; ++pk)
+#pragma unroll
+                for (int e = 0; e < N; ++e) acc[h][pk][e] *= corr[h];
+        // values: group vg takes keys vg, vg + value_step, ...; a key behind the last one has weight 0
+        const int keys_here = min(32, pos - key0 + 1);
+#pragma unroll 2
+        for (int j0 = 0; j0 < keys_here; j0 += value_step) {
+            const int j = j0 + vg;                    // (j < 32 always)
+            const T* vp = vbase + voffs[j];
+            float pj[HPW];
+#pragma unroll
+            for (int h = 0; h < HPW; ++h) pj[h] = ps[h * 32 + j];
+#pragma unroll
+            for (int pk = 0; pk < NP; ++pk) {
+                const int col = (pk * lv + vs) * N;
+                if (col < vdim) {
+                    float vv[N];
+                    Packet<T>::load(vp + col, vv);
+#pragma unroll
+                    for (int h = 0; h < HPW; ++h)
+#pragma unroll
+                        for (int e = 0; e < N; ++e) acc[h][pk][e] = fmaf(pj[h], vv[e], acc[h][pk][e]);
+                }
+            }
+        }
+    }
+    // the groups' partial sums, in a fixed butterfly
+    for (int o = lv; o < 32; o <<= 1)
+#pragma unroll
+        for (int h = 0; h < HPW; ++h)
+#pragma unroll
+            for (int pk = 0; pk < NP; ++pk)
+#pragma unroll
+                for (int e = 0; e < N; ++e) acc[h][pk][e] += __shfl_xor_sync(0xffffffffu, acc[h][pk][e], o);
+    if (vg != 0) return;
+#pragma unroll
+    for (int h = 0; h < HPW; ++h) {
+        const float inv = 1.0f / fmaxf(l[h], 1.0e-30f);
+        T* orow = out + (int64_t)row * out_stride + (int64_t)(head0 + h) * vdim;
+        const T* grow = gate == nullptr ? nullptr : gate + (int64_t)row * gate_stride + (int64_t)(head0 + h) * vdim;
+#pragma unroll
+        for (int pk = 0; pk < NP; ++pk) {
+            const int col = (pk * lv + vs) * N;
+            if (col < vdim) {
+                float value[N];
+#pragma unroll
+                for (int e = 0; e < N; ++e) value[e] = acc[h][pk][e] * inv;
+                if (grow != nullptr) {
+                    float gv[N];
+                    Packet<T>::load(grow + col, gv);
+#pragma unroll
+                    for (int e = 0; e < N; ++e) value[e] *= __fdividef(1.0f, 1.0f + __expf(-gv[e]));
+                }
+                Packet<T>::store(orow + col, value);
+            }
+        }
+    }
+}
+
+template <typename T, int HPW, int NP>
+int launch_packets_as(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out,
+                      int64_t out_stride, const void* cache, const int* positions, const int* seq_of_row,
+                      const int* block_table, int bt_stride, int rows, int heads, int kv_heads, int dim, int vdim,
+                      int page_size, int mask_kind, int mask_size, int sink, float scale, cudaStream_t stream) {
+    constexpr int N = Packet<T>::N;
+    int lv = 1;
+    while (lv < 32 && lv * NP < vdim / N) lv <<= 1;
+    const dim3 grid((rows + kRowsPerBlock - 1) / kRowsPerBlock, heads / HPW);
+    const size_t smem = kRowsPerBlock * (32 * sizeof(int64_t) + (size_t)HPW * (32 + dim) * sizeof(float));
+    auto kernel = attention_masked_packets_kernel<T, HPW, NP>;
+    if (smem > 40 * 1024) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+    }
+    kernel<<<grid, kRowsPerBlock * 32, smem, stream>>>((const T*)q, q_stride, (const T*)gate, gate_stride, (T*)out,
+                                                       out_stride, (const T*)cache, positions, seq_of_row, block_table,
+                                                       bt_stride, rows, heads, kv_heads, dim, vdim, page_size,
+                                                       mask_kind, mask_size, sink, scale, lv);
+    return tb_launch_status();
+}
+
+template <typename T>
+int launch_packets(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out, int64_t out_stride,
+                   const void* cache, const int* positions, const int* seq_of_row, const int* block_table,
+                   int bt_stride, int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind,
+                   int mask_size, int sink, float scale, cudaStream_t stream) {
+    const int per = heads / kv_heads;
+    const bool two = vdim / Packet<T>::N > 32;        // more value packets than lanes: two a lane
+#define TB_PACKETS(HPW, NP)                                                                                          \
+    return launch_packets_as<T, HPW, NP>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions,          \
+                                         seq_of_row, block_table, bt_stride, rows, heads, kv_heads, dim, vdim,       \
+                                         page_size, mask_kind, mask_size, sink, scale, stream)
+    if (per % 4 == 0 && !two) TB_PACKETS(4, 1);
+    if (per % 2 == 0) { if (two) TB_PACKETS(2, 2); else TB_PACKETS(2, 1); }
+    if (two) TB_PACKETS(1, 2);
+    TB_PACKETS(1, 1);
+#undef TB_PACKETS
+}
+
 template <typename T, bool VEC>
 int launch_vec(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out, int64_t out_stride,
                const void* cache, const int* positions, const int* seq_of_row, const int* block_table, int bt_stride,
@@ -143,6 +346,13 @@ int launch(const void* q, int64_t q_stride, const void* gate, int64_t gate_strid
            float scale, cudaStream_t stream) {
     // 16-byte key loads need every key row to start on a 16-byte boundary
     const bool vec = dim % Packet<T>::N == 0 && vdim % Packet<T>::N == 0 && (uintptr_t)cache % 16 == 0;
+    const uintptr_t bits = (uintptr_t)q | (uintptr_t)gate | (uintptr_t)out;
+    const bool rows_in_packets = bits % 16 == 0 && q_stride % Packet<T>::N == 0 && out_stride % Packet<T>::N == 0 &&
+                                 (gate == nullptr || gate_stride % Packet<T>::N == 0);
+    if (vec && rows_in_packets && vdim <= 64 * Packet<T>::N && dim <= 64 * Packet<T>::N)
+        return launch_packets<T>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions, seq_of_row,
+                                 block_table, bt_stride, rows, heads, kv_heads, dim, vdim, page_size, mask_kind,
+                                 mask_size, sink, scale, stream);
     if (vec)
         return launch_vec<T, true>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions, seq_of_row,
                                    block_table, bt_stride, rows, heads, kv_heads, dim, vdim, page_size, mask_kind,

@@ -5,7 +5,7 @@
 // A projected row holds, side by side, H query heads of d numbers, G key heads of d numbers and G value heads of
 // dv numbers (anything behind them in the row, an output gate for instance, is left alone).  Per channel c:
 //
-//   y[t] = sum_{j < J} taps[c, j] * u[t - (J - 1) + j]        (u = 0 before the sequence starts)
+//   y[t] = sum_{j < J} taps[j, c] * u[t - (J - 1) + j]        (u = 0 before the sequence starts)
 //
 // where u at positions before this step's first token comes from the request's convolution state (the last J - 1
 // projected rows, 32-bit, [slot][J - 1][channels]; position p of the request lies at index p - (begin - (J - 1))).
@@ -14,7 +14,8 @@
 // into the pages: a page is [G][page_size][d] keys followed by [G][page_size][dv] values.
 //
 // All arithmetic is 32-bit; each stored value is rounded once.  A thread owns one pair of neighbouring channels
-// of one row, so a row's values do not depend on the batch around it.
+// of one row (or, in the packet kernel, one 16-byte packet of channels of a few rows in turn), and every channel's
+// sum runs over its taps in the same order, so a row's values do not depend on the batch around it.
 //
 // The state is renewed (to the last J - 1 projected rows of the request) by tb_conv_state_update after the
 // convolution of a step has read it, or, in a step where every sequence brings one row (`single` != 0), by the
@@ -95,8 +96,8 @@ conv_rope_cache_kernel(const T* __restrict__ proj, int64_t proj_stride, const fl
 #pragma unroll
     for (int j = 0; j < kMaxTaps; ++j) {
         if (j < J) {
-            y0 = fmaf(taps[(int64_t)c0 * J + j], u0[j], y0);
-            if (has_second) y1 = fmaf(taps[(int64_t)(c0 + 1) * J + j], u1[j], y1);
+            y0 = fmaf(taps[(int64_t)j * g.channels + c0], u0[j], y0);
+            if (has_second) y1 = fmaf(taps[(int64_t)j * g.channels + c0 + 1], u1[j], y1);
         }
     }
     if (SINGLE && J > 1) {
@@ -133,6 +134,123 @@ conv_rope_cache_kernel(const T* __restrict__ proj, int64_t proj_stride, const fl
     else dst += (int64_t)g.kv_heads * g.page_size * g.dim + ((int64_t)head * g.page_size + in_page) * g.vdim + e0;
     Elem<T>::store(dst, y0);
     if (has_second) Elem<T>::store(dst + 1, y1);
+}
+
+// The same work in 16-byte packets, for head sizes that are multiples of a packet (8 bfloat16, 4 floats) and up to
+// four taps: a thread owns one packet of channels for kRowTile neighbouring rows, holds that packet's taps in
+// registers, and reads J packets per row (rows of this step) or J runs of 32-bit numbers (rows of the state).
+constexpr int kRowTile = 4;
+
+template <int N>
+__device__ __forceinline__ void load_floats(const float* p, float* v) {
+#pragma unroll
+    for (int e = 0; e < N; e += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p + e);
+        v[e] = t.x; v[e + 1] = t.y; v[e + 2] = t.z; v[e + 3] = t.w;
+    }
+}
+template <int N>
+__device__ __forceinline__ void store_floats(float* p, const float* v) {
+#pragma unroll
+    for (int e = 0; e < N; e += 4) *reinterpret_cast<float4*>(p + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+}
+
+template <typename T, bool SINGLE, int J>
+__global__ void __launch_bounds__(128)
+conv_rope_cache_packets_kernel(const T* __restrict__ proj, int64_t proj_stride, const float* __restrict__ taps,
+                               float* __restrict__ state, T* __restrict__ q_out, int64_t q_stride,
+                               T* __restrict__ cache, const int* __restrict__ positions,
+                               const int* __restrict__ seq_of_row, const int* __restrict__ row_start,
+                               const int* __restrict__ seq_begin, const int* __restrict__ state_slots,
+                               const int* __restrict__ block_table, int bt_stride, const float* __restrict__ inv_freq,
+                               ConvGeometry g, int write_kv, int rows) {
+    constexpr int N = Packet<T>::N;
+    const int packet = blockIdx.y * blockDim.x + threadIdx.x;
+    if (packet >= g.channels / N) return;
+    const int c0 = packet * N;
+    int segment, head, e0;
+    if (c0 < g.heads * g.dim) {
+        segment = 0; head = c0 / g.dim; e0 = c0 % g.dim;
+    } else if (c0 < (g.heads + g.kv_heads) * g.dim) {
+        segment = 1; head = (c0 - g.heads * g.dim) / g.dim; e0 = (c0 - g.heads * g.dim) % g.dim;
+    } else {
+        const int local = c0 - (g.heads + g.kv_heads) * g.dim;
+        segment = 2; head = local / g.vdim; e0 = local % g.vdim;
+    }
+    float w[J][N];                                   // the packet's taps: neighbouring lanes read neighbouring packets
+#pragma unroll
+    for (int j = 0; j < J; ++j) load_floats<N>(taps + (int64_t)j * g.channels + c0, w[j]);
+    const bool rotates = segment < 2 && e0 < g.rot_dims;
+    const int64_t page_elems = (int64_t)g.kv_heads * g.page_size * (g.dim + g.vdim);
+
+    // what the rows of the tile are, asked for at once (each is a chain of two or three dependent loads)
+    int row_pos[kRowTile], row_begin[kRowTile], row_first[kRowTile], row_slot[kRowTile], row_page[kRowTile];
+#pragma unroll
+    for (int r = 0; r < kRowTile; ++r) {
+        const int row = min(blockIdx.x * kRowTile + r, rows - 1);
+        const int seq = seq_of_row[row];
+        row_pos[r] = positions[row];
+        row_begin[r] = seq_begin[seq];
+        row_first[r] = row_start[seq];
+        row_slot[r] = state_slots[seq];
+        row_page[r] = (segment != 0 && write_kv) ? block_table[(int64_t)seq * bt_stride + row_pos[r] / g.page_size] : 0;
+    }
+#pragma unroll
+    for (int r = 0; r < kRowTile; ++r) {
+        const int row = blockIdx.x * kRowTile + r;
+        if (row >= rows) return;
+        const int pos = row_pos[r];
+        const int begin = row_begin[r];
+        const int first_row = row_first[r];
+        float* st = state + (int64_t)row_slot[r] * (J - 1) * g.channels + c0;
+        float u[J][N];
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            const int p = pos - (J - 1) + j;
+            if (p >= begin) {
+                Packet<T>::load(proj + (int64_t)(first_row + (p - begin)) * proj_stride + c0, u[j]);
+            } else if (p >= 0) {
+                load_floats<N>(st + (int64_t)(p - (begin - (J - 1))) * g.channels, u[j]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < N; ++e) u[j][e] = 0.0f;
+            }
+        }
+        float y[N];
+#pragma unroll
+        for (int e = 0; e < N; ++e) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < J; ++j) sum = fmaf(w[j][e], u[j][e], sum);
+            y[e] = sum;
+        }
+        if (SINGLE) {
+#pragma unroll
+            for (int j = 1; j < J; ++j) store_floats<N>(st + (int64_t)(j - 1) * g.channels, u[j]);
+        }
+        if (rotates) {
+#pragma unroll
+            for (int e = 0; e < N; e += 2) {
+                if (e0 + e < g.rot_dims) {
+                    float sn, cs;
+                    sincosf((float)pos * inv_freq[(e0 + e) >> 1], &sn, &cs);
+                    const float r0 = y[e] * cs - y[e + 1] * sn;
+                    const float r1 = y[e + 1] * cs + y[e] * sn;
+                    y[e] = r0;
+                    y[e + 1] = r1;
+                }
+            }
+        }
+        if (segment == 0) {
+            Packet<T>::store(q_out + (int64_t)row * q_stride + c0, y);
+        } else if (write_kv) {
+            const int in_page = pos % g.page_size;
+            T* dst = cache + (int64_t)row_page[r] * page_elems;
+            if (segment == 1) dst += ((int64_t)head * g.page_size + in_page) * g.dim + e0;
+            else dst += (int64_t)g.kv_heads * g.page_size * g.dim + ((int64_t)head * g.page_size + in_page) * g.vdim + e0;
+            Packet<T>::store(dst, y);
+        }
+    }
 }
 
 // New state of every sequence of the step: index i holds the projected row of position begin + n - (J - 1) + i,
@@ -181,6 +299,22 @@ int launch(const void* proj, int64_t proj_stride, const float* taps, float* stat
            void* cache, const int* positions, const int* seq_of_row, const int* row_start, const int* seq_begin,
            const int* state_slots, const int* block_table, int bt_stride, const float* inv_freq, int rows,
            const ConvGeometry& g, int write_kv, int single, cudaStream_t stream) {
+    constexpr int N = Packet<T>::N;
+    const uintptr_t bits = (uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)state | (uintptr_t)taps;
+    if (g.dim % N == 0 && g.vdim % N == 0 && g.taps <= 4 && proj_stride % N == 0 && q_stride % N == 0 &&
+        bits % 16 == 0) {
+        const dim3 tiles((rows + kRowTile - 1) / kRowTile, (g.channels / N + 127) / 128);
+#define TB_CONV(S, J)                                                                                                    conv_rope_cache_packets_kernel<T, S, J><<<tiles, 128, 0, stream>>>(                                                      (const T*)proj, proj_stride, taps, state, (T*)q_out, q_stride, (T*)cache, positions, seq_of_row, row_start,           seq_begin, state_slots, block_table, bt_stride, inv_freq, g, write_kv, rows)
+        if (single) {
+            if (g.taps == 1) TB_CONV(true, 1); else if (g.taps == 2) TB_CONV(true, 2);
+            else if (g.taps == 3) TB_CONV(true, 3); else TB_CONV(true, 4);
+        } else {
+            if (g.taps == 1) TB_CONV(false, 1); else if (g.taps == 2) TB_CONV(false, 2);
+            else if (g.taps == 3) TB_CONV(false, 3); else TB_CONV(false, 4);
+        }
+#undef TB_CONV
+        return tb_launch_status();
+    }
     const int total = g.q_pairs + g.k_pairs + g.v_pairs;
     const dim3 grid(rows, (total + 127) / 128);
     if (single)
@@ -196,7 +330,8 @@ int launch(const void* proj, int64_t proj_stride, const float* taps, float* stat
 
 }  // namespace
 
-// proj: [rows, >= channels] with row stride proj_stride (elements); taps: 32-bit [channels, taps];
+// proj: [rows, >= channels] with row stride proj_stride (elements); taps: 32-bit [taps, channels] (tap j of
+// every channel side by side: tap taps - 1 multiplies the row itself, tap 0 the oldest);
 // state: 32-bit [slots, taps - 1, channels]; q_out: [rows, heads * dim] with row stride q_stride;
 // cache: this layer's pages; inv_freq: 32-bit [rot_dims / 2] (may be null when rot_dims is 0).
 // single != 0: every sequence of the step brings exactly one row, and the state is renewed here.

@@ -137,7 +137,7 @@ int launch_kernel(const void* x, const void* upd, const float* w, void* y, void*
     int threads = 32;
     while (threads < 512 && threads * per_thread < width) threads <<= 1;
     auto kernel = rms_norm_kernel<T, ADD, VEC>;
-    if (smem > 48 * 1024) {
+    if (smem > 40 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
     }
@@ -202,6 +202,64 @@ __global__ void group_rms_norm_kernel(const float* __restrict__ res, const U* __
     for (int j = threadIdx.x; j < part; j += blockDim.x) Elem<T>::store(y + base + j, part_cache[j] * inv * wp[j]);
 }
 
+// Four numbers of a part per thread and iteration: 16-byte loads of the stream, 16- or 8-byte loads of the update and
+// stores of the output (parts of a multiple of four numbers, aligned buffers).
+template <typename U>
+__device__ __forceinline__ void load4(const U* p, float* v);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float* v) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float* v) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+}
+__device__ __forceinline__ void store4(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float* v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+}
+
+template <typename U, typename T, bool ADD>
+__global__ void __launch_bounds__(1024)
+group_rms_norm4_kernel(const float* __restrict__ res, const U* __restrict__ upd, const float* __restrict__ w,
+                       T* __restrict__ y, float* __restrict__ res_out, int part, int groups, float eps) {
+    extern __shared__ __align__(16) float part_cache[];
+    __shared__ float scratch[32];
+    const int64_t base = (int64_t)blockIdx.x * part;
+    const float* wp = w + (int64_t)(blockIdx.x % groups) * part;
+    float ss = 0.0f;
+    for (int j = threadIdx.x * 4; j < part; j += blockDim.x * 4) {
+        float v[4];
+        load4<float>(res + base + j, v);
+        if (ADD) {
+            float u[4];
+            load4<U>(upd + base + j, u);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] += u[e];
+            store4(res_out + base + j, v);
+        }
+        store4(part_cache + j, v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss = fmaf(v[e], v[e], ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)part + eps);
+    for (int j = threadIdx.x * 4; j < part; j += blockDim.x * 4) {      // each thread rereads what it wrote
+        float v[4], wv[4];
+        load4<float>(part_cache + j, v);
+        load4<float>(wp + j, wv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = v[e] * inv * wv[e];
+        store4(y + base + j, v);
+    }
+}
+
 template <typename U, typename T>
 int launch_group(const float* res, const void* upd, const float* w, void* y, float* res_out, int rows, int width,
                  int groups, float eps, cudaStream_t stream) {
@@ -211,13 +269,27 @@ int launch_group(const float* res, const void* upd, const float* w, void* y, flo
     int threads = 32;
     while (threads < 512 && threads * 4 < part) threads <<= 1;
     const dim3 grid((unsigned)((int64_t)rows * groups));
+    const uintptr_t bits = (uintptr_t)res | (uintptr_t)upd | (uintptr_t)w | (uintptr_t)y | (uintptr_t)res_out;
+    if (part % 4 == 0 && bits % 16 == 0) {        // (which kernel runs depends on the width and alignment alone)
+        const int threads4 = part / 4 >= 1024 ? 1024 : ((part / 4 + 31) / 32) * 32;
+        if (upd != nullptr) {
+            auto kernel = group_rms_norm4_kernel<U, T, true>;
+            if (smem > 40 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            kernel<<<grid, threads4, smem, stream>>>(res, (const U*)upd, w, (T*)y, res_out, part, groups, eps);
+        } else {
+            auto kernel = group_rms_norm4_kernel<U, T, false>;
+            if (smem > 40 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            kernel<<<grid, threads4, smem, stream>>>(res, nullptr, w, (T*)y, nullptr, part, groups, eps);
+        }
+        return tb_launch_status();
+    }
     if (upd != nullptr) {
         auto kernel = group_rms_norm_kernel<U, T, true>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 40 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kernel<<<grid, threads, smem, stream>>>(res, (const U*)upd, w, (T*)y, res_out, part, groups, eps);
     } else {
         auto kernel = group_rms_norm_kernel<U, T, false>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 40 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kernel<<<grid, threads, smem, stream>>>(res, nullptr, w, (T*)y, nullptr, part, groups, eps);
     }
     return tb_launch_status();

@@ -773,18 +773,18 @@ def conv_rope_cache(proj: torch.Tensor, taps: torch.Tensor, state: Optional[torc
                     seq_begin: torch.Tensor, state_slots: torch.Tensor, block_table: torch.Tensor,
                     inv_freq: Optional[torch.Tensor], *, num_seqs: int, heads: int, kv_heads: int, dim: int, vdim: int,
                     rot_dims: int, page_size: int, write_kv: bool, single: bool) -> None:
-    """Short causal convolutions over the q, k and v channels of ``proj`` (``taps`` float32 ``[channels, J]``,
+    """Short causal convolutions over the q, k and v channels of ``proj`` (``taps`` float32 ``[J, channels]``,
     ``state`` float32 ``[slots, J - 1, channels]``), pairwise rotation of the first ``rot_dims`` numbers of every
     query and key head, queries into ``q_out``, keys and values into the pages of ``cache``.  ``single``: every
     sequence brings one row (the state is renewed inside the kernel); otherwise a second launch renews it."""
     _cuda(proj, taps, state, q_out, cache, positions, seq_of_row, row_start, seq_begin, state_slots, block_table, inv_freq)
     rows = q_out.shape[0]
     channels = heads * dim + kv_heads * (dim + vdim)
-    count = taps.shape[1]
+    count = taps.shape[0]
     _need(proj.stride(1) == 1 and proj.shape[1] >= channels and proj.shape[0] == rows, "conv_rope_cache proj")
     _need(q_out.stride(1) == 1 and q_out.shape[1] == heads * dim and q_out.dtype == proj.dtype, "conv_rope_cache q_out")
     _need(cache.dtype == proj.dtype and cache.is_contiguous(), "conv_rope_cache cache dtype")
-    _need(taps.dtype == torch.float32 and taps.is_contiguous() and taps.shape[0] == channels, "conv_rope_cache taps")
+    _need(taps.dtype == torch.float32 and taps.is_contiguous() and taps.shape[1] == channels, "conv_rope_cache taps")
     if count > 1:
         _need(state is not None and state.dtype == torch.float32 and state.is_contiguous()
               and tuple(state.shape[1:]) == (count - 1, channels), "conv_rope_cache state")

@@ -76,8 +76,9 @@ class ConvAttention(Mixer):
         rows = [tensors["q"], tensors["k"], tensors["v"]] + ([tensors["g"]] if self.gated else [])
         self.in_proj = Linear(torch.cat(rows, dim=0), runtime)
         self.o_proj = Linear(tensors["o"], runtime)
+        # [taps, channels]: tap j of every channel side by side, as the kernel reads them
         self.conv_taps = torch.cat([tensors["q_conv"], tensors["k_conv"], tensors["v_conv"]], dim=0).to(
-            device=runtime.device, dtype=torch.float32).contiguous()
+            device=runtime.device, dtype=torch.float32).t().contiguous()
         position_spec = spec.children.get("position") or PartSpec.make("none")
         self.position = POSITION_ENCODINGS.get(position_spec.kind)(position_spec, {}, runtime)
         if self.position.kind not in ("rotary_pairs", "none"):

@@ -30,7 +30,7 @@ def dev():
 # ----------------------------------------------------------------------------- mechanisms alone
 
 
-@pytest.mark.parametrize("groups,width", [(1, 48), (2, 50), (3, 33), (4, 4096)])
+@pytest.mark.parametrize("groups,width", [(1, 48), (2, 50), (3, 33), (4, 4096), (1, 12288)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_grouped_norm_alone_and_with_the_addition(groups, width, out_dtype):
     from tesseract_b200 import kernels
@@ -54,7 +54,7 @@ def test_grouped_norm_alone_and_with_the_addition(groups, width, out_dtype):
                               rtol=tol, atol=tol)
 
 
-@pytest.mark.parametrize("width", [5, 72, 257, 11008])
+@pytest.mark.parametrize("width", [5, 72, 257, 12288, 14000])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_polynorm_alone(width, dtype):
     from tesseract_b200 import kernels
@@ -192,7 +192,7 @@ def test_convolution_rotation_and_cache_write(dtype, taps, heads, kv_heads, d, d
         begin = torch.tensor([done[s] for s in seqs], dtype=torch.int32, device=dev())
         slot = torch.tensor([slots[s] for s in seqs], dtype=torch.int32, device=dev())
         q = torch.empty(rows, heads * d, dtype=dtype, device=dev())
-        kernels.conv_rope_cache(proj, w.to(dev()), state, q, storage, positions, seq_of_row, row_start, begin, slot,
+        kernels.conv_rope_cache(proj, w.t().contiguous().to(dev()), state, q, storage, positions, seq_of_row, row_start, begin, slot,
                                 tables[seqs].to(dev()), inv_freq.to(dev()), num_seqs=len(seqs), heads=heads,
                                 kv_heads=kv_heads, dim=d, vdim=dv, rot_dims=rot, page_size=page, write_kv=True,
                                 single=max(new) == 1)
@@ -427,9 +427,9 @@ def test_greedy_generation_through_the_scheduler(folders, name, dtype, graphs):
     from tesseract_b200 import LLM, SamplingParams
 
     config, tensors = plain.load_folder(folders(name))
-    prompts = [random_tokens(config["vocab"], n, seed=n) for n in (3, 19, 40, 1)]
+    prompts = [random_tokens(config["vocab"], n, seed=n) for n in (3, 19, 75, 1)]
     steps = 24
-    llm = LLM(folders(name), dtype=dtype, kv_capacity_tokens=1024, max_running=3, prefill_chunk_tokens=16,
+    llm = LLM(folders(name), dtype=dtype, kv_capacity_tokens=1024, max_running=3, prefill_chunk_tokens=32,
               cuda_graphs=graphs)
     outs = llm.generate(prompts, SamplingParams(max_tokens=steps, temperature=0.0, ignore_eos=True))
     for prompt, out in zip(prompts, outs):
