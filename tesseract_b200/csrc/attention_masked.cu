@@ -23,7 +23,9 @@
 // but a few of the same keys and meet in L1.  Scores: a lane a key, the key's packets against the queries in
 // shared memory (read four numbers at a time).  Values: the warp is cut into groups of lanes that share a value
 // row, a lane a packet of columns, the weights passed through shared memory; the groups' partial sums meet at the
-// end in a fixed butterfly.  The element kernel takes every other size, a number at a time.
+// end in a fixed butterfly.  In a step of few rows (decoded ones) a block is one row instead, and its four warps
+// share the row's keys; which of the two runs depends on the number of rows of the step, so a row's values are the
+// same in every batch up to the order of a few sums.  The element kernel takes every other size, a number at a time.
 #include "common.cuh"
 
 namespace {
@@ -39,6 +41,8 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
                         const int* __restrict__ block_table, int bt_stride, int heads, int kv_heads, int dim, int vdim,
                         int page_size, int mask_kind, int mask_size, int sink, float scale) {
     extern __shared__ float q_smem[];                 // kWarps * dim
+    pdl_trigger();
+    pdl_wait();                                       // queries, pages and the step's metadata come from kernels in front
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x;
     const int head = blockIdx.y * kWarps + warp;
@@ -125,11 +129,14 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
 
 
 constexpr int kRowsPerBlock = 8;      // warps of a block: neighbouring rows of the same heads
+constexpr int kSplitWarps = 4;        // warps of a block that share one row's keys (steps of few rows)
 
-// HPW: query heads of one kv head that a warp takes together (1, 2 or 4); NP: packets of value columns per lane;
+// HPW: query heads of one kv head that a warp takes together (1 to 4, a divisor of the heads per kv head); NP: packets of value columns per lane;
 // lv: lanes that share a value row in the value phase (a power of two).
-template <typename T, int HPW, int NP>
-__global__ void __launch_bounds__(kRowsPerBlock * 32)
+// SPLIT: a block is ONE row (a step of few rows, decoded ones for instance): its four warps take every fourth
+// block of 32 keys each and their partial results (running maximum, sum, accumulator) meet in shared memory.
+template <typename T, int HPW, int NP, bool SPLIT>
+__global__ void __launch_bounds__(kRowsPerBlock * 32, 3)
 attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict__ gate,
                                 int64_t gate_stride, T* __restrict__ out, int64_t out_stride,
                                 const T* __restrict__ cache, const int* __restrict__ positions,
@@ -137,11 +144,14 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
                                 int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind,
                                 int mask_size, int sink, float scale, int lv) {
     constexpr int N = Packet<T>::N;
+    constexpr int WARPS = SPLIT ? kSplitWarps : kRowsPerBlock;
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_trigger();
+    pdl_wait();                                       // queries, pages and the step's metadata come from kernels in front
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * kRowsPerBlock + warp;
+    const int row = SPLIT ? blockIdx.x : blockIdx.x * WARPS + warp;
     const int head0 = blockIdx.y * HPW;
-    if (row >= rows) return;                          // the whole warp leaves; no block-wide barrier below
+    if (!SPLIT && row >= rows) return;                // the whole warp leaves; no block-wide barrier on this path
     const size_t per_warp = 32 * sizeof(int64_t) + (size_t)HPW * (32 + dim) * sizeof(float);
     int64_t* voffs = reinterpret_cast<int64_t*>(smem_raw + warp * per_warp);
     float* ps = reinterpret_cast<float*>(voffs + 32);         // [HPW][32]
@@ -165,17 +175,18 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
     const int value_step = 32 / lv;
 
     float m[HPW], l[HPW], acc[HPW][NP][N];
+    const bool starts = sink && (!SPLIT || warp == 0);        // the sink is the start of one running softmax
 #pragma unroll
     for (int h = 0; h < HPW; ++h) {
-        m[h] = sink ? 0.0f : -1.0e30f;
-        l[h] = sink ? 1.0f : 0.0f;
+        m[h] = starts ? 0.0f : -1.0e30f;
+        l[h] = starts ? 1.0f : 0.0f;
 #pragma unroll
         for (int pk = 0; pk < NP; ++pk)
 #pragma unroll
             for (int e = 0; e < N; ++e) acc[h][pk][e] = 0.0f;
     }
 
-    for (int key0 = first_key; key0 <= pos; key0 += 32) {
+    for (int key0 = first_key + (SPLIT ? 32 * warp : 0); key0 <= pos; key0 += SPLIT ? 32 * WARPS : 32) {
         const int key = key0 + lane;
         const bool valid = key <= pos;
         const int k = valid ? key : pos;              // (a lane behind the last key points at the last key)
@@ -253,6 +264,55 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
             for (int pk = 0; pk < NP; ++pk)
 #pragma unroll
                 for (int e = 0; e < N; ++e) acc[h][pk][e] += __shfl_xor_sync(0xffffffffu, acc[h][pk][e], o);
+    if (SPLIT) {
+        // every warp leaves (maximum, sum, accumulator) of its share of the keys; warp 0 adds them up in warp order
+        float* parts = reinterpret_cast<float*>(smem_raw + WARPS * per_warp);     // [warps][HPW][vdim + 2]
+        const int stride = vdim + 2;
+        if (vg == 0) {
+#pragma unroll
+            for (int h = 0; h < HPW; ++h) {
+                float* mine = parts + ((size_t)warp * HPW + h) * stride;
+                if (vs == 0) {
+                    mine[vdim] = m[h];
+                    mine[vdim + 1] = l[h];
+                }
+#pragma unroll
+                for (int pk = 0; pk < NP; ++pk) {
+                    const int col = (pk * lv + vs) * N;
+                    if (col < vdim) {
+#pragma unroll
+                        for (int e = 0; e < N; ++e) mine[col + e] = acc[h][pk][e];
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        if (warp != 0 || vg != 0) return;
+#pragma unroll
+        for (int h = 0; h < HPW; ++h) {
+            float top = -1.0e30f;
+            for (int w = 0; w < WARPS; ++w) top = fmaxf(top, parts[((size_t)w * HPW + h) * stride + vdim]);
+            float total = 0.0f;
+#pragma unroll
+            for (int pk = 0; pk < NP; ++pk)
+#pragma unroll
+                for (int e = 0; e < N; ++e) acc[h][pk][e] = 0.0f;
+            for (int w = 0; w < WARPS; ++w) {
+                const float* theirs = parts + ((size_t)w * HPW + h) * stride;
+                const float weight = __expf(theirs[vdim] - top);
+                total = fmaf(theirs[vdim + 1], weight, total);
+#pragma unroll
+                for (int pk = 0; pk < NP; ++pk) {
+                    const int col = (pk * lv + vs) * N;
+                    if (col < vdim) {
+#pragma unroll
+                        for (int e = 0; e < N; ++e) acc[h][pk][e] = fmaf(theirs[col + e], weight, acc[h][pk][e]);
+                    }
+                }
+            }
+            l[h] = total;
+        }
+    }
     if (vg != 0) return;
 #pragma unroll
     for (int h = 0; h < HPW; ++h) {
@@ -278,7 +338,9 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
     }
 }
 
-template <typename T, int HPW, int NP>
+constexpr int kSplitMaxRows = 256;     // steps of at most this many rows give every row a block of its own
+
+template <typename T, int HPW, int NP, bool SPLIT>
 int launch_packets_as(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out,
                       int64_t out_stride, const void* cache, const int* positions, const int* seq_of_row,
                       const int* block_table, int bt_stride, int rows, int heads, int kv_heads, int dim, int vdim,
@@ -286,18 +348,20 @@ int launch_packets_as(const void* q, int64_t q_stride, const void* gate, int64_t
     constexpr int N = Packet<T>::N;
     int lv = 1;
     while (lv < 32 && lv * NP < vdim / N) lv <<= 1;
-    const dim3 grid((rows + kRowsPerBlock - 1) / kRowsPerBlock, heads / HPW);
-    const size_t smem = kRowsPerBlock * (32 * sizeof(int64_t) + (size_t)HPW * (32 + dim) * sizeof(float));
-    auto kernel = attention_masked_packets_kernel<T, HPW, NP>;
+    constexpr int WARPS = SPLIT ? kSplitWarps : kRowsPerBlock;
+    const dim3 grid(SPLIT ? rows : (rows + WARPS - 1) / WARPS, heads / HPW);
+    const size_t smem = WARPS * (32 * sizeof(int64_t) + (size_t)HPW * (32 + dim) * sizeof(float)) +
+                        (SPLIT ? (size_t)WARPS * HPW * (vdim + 2) * sizeof(float) : 0);
+    auto kernel = attention_masked_packets_kernel<T, HPW, NP, SPLIT>;
     if (smem > 40 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
     }
-    kernel<<<grid, kRowsPerBlock * 32, smem, stream>>>((const T*)q, q_stride, (const T*)gate, gate_stride, (T*)out,
-                                                       out_stride, (const T*)cache, positions, seq_of_row, block_table,
-                                                       bt_stride, rows, heads, kv_heads, dim, vdim, page_size,
-                                                       mask_kind, mask_size, sink, scale, lv);
-    return tb_launch_status();
+    cudaError_t launched = tb_launch_pdl(kernel, grid, dim3(WARPS * 32), smem, stream, (const T*)q, q_stride,
+                                         (const T*)gate, gate_stride, (T*)out, out_stride, (const T*)cache, positions,
+                                         seq_of_row, block_table, bt_stride, rows, heads, kv_heads, dim, vdim,
+                                         page_size, mask_kind, mask_size, sink, scale, lv);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
 template <typename T>
@@ -308,10 +372,17 @@ int launch_packets(const void* q, int64_t q_stride, const void* gate, int64_t ga
     const int per = heads / kv_heads;
     const bool two = vdim / Packet<T>::N > 32;        // more value packets than lanes: two a lane
 #define TB_PACKETS(HPW, NP)                                                                                          \
-    return launch_packets_as<T, HPW, NP>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions,          \
-                                         seq_of_row, block_table, bt_stride, rows, heads, kv_heads, dim, vdim,       \
-                                         page_size, mask_kind, mask_size, sink, scale, stream)
+    return rows <= kSplitMaxRows                                                                                     \
+               ? launch_packets_as<T, HPW, NP, true>(q, q_stride, gate, gate_stride, out, out_stride, cache,         \
+                                                     positions, seq_of_row, block_table, bt_stride, rows, heads,     \
+                                                     kv_heads, dim, vdim, page_size, mask_kind, mask_size, sink,     \
+                                                     scale, stream)                                                  \
+               : launch_packets_as<T, HPW, NP, false>(q, q_stride, gate, gate_stride, out, out_stride, cache,        \
+                                                      positions, seq_of_row, block_table, bt_stride, rows, heads,    \
+                                                      kv_heads, dim, vdim, page_size, mask_kind, mask_size, sink,    \
+                                                      scale, stream)
     if (per % 4 == 0 && !two) TB_PACKETS(4, 1);
+    if (per % 3 == 0 && !two) TB_PACKETS(3, 1);
     if (per % 2 == 0) { if (two) TB_PACKETS(2, 2); else TB_PACKETS(2, 1); }
     if (two) TB_PACKETS(1, 2);
     TB_PACKETS(1, 1);
@@ -326,9 +397,9 @@ int launch_vec(const void* q, int64_t q_stride, const void* gate, int64_t gate_s
     const dim3 grid(rows, (heads + kWarps - 1) / kWarps);
     const size_t smem = (size_t)kWarps * dim * sizeof(float);
 #define TB_LAUNCH(NCV)                                                                                              \
-    attention_masked_kernel<T, NCV, VEC><<<grid, kWarps * 32, smem, stream>>>(                                      \
-        (const T*)q, q_stride, (const T*)gate, gate_stride, (T*)out, out_stride, (const T*)cache, positions,        \
-        seq_of_row, block_table, bt_stride, heads, kv_heads, dim, vdim, page_size, mask_kind, mask_size, sink, scale)
+    tb_launch_pdl(attention_masked_kernel<T, NCV, VEC>, grid, dim3(kWarps * 32), smem, stream, (const T*)q, q_stride,   \
+                  (const T*)gate, gate_stride, (T*)out, out_stride, (const T*)cache, positions, seq_of_row,         \
+                  block_table, bt_stride, heads, kv_heads, dim, vdim, page_size, mask_kind, mask_size, sink, scale)
     if (vdim <= 32) TB_LAUNCH(1);
     else if (vdim <= 64) TB_LAUNCH(2);
     else if (vdim <= 96) TB_LAUNCH(3);

@@ -43,6 +43,8 @@ conv_rope_cache_kernel(const T* __restrict__ proj, int64_t proj_stride, const fl
                        const int* __restrict__ row_start, const int* __restrict__ seq_begin,
                        const int* __restrict__ state_slots, const int* __restrict__ block_table, int bt_stride,
                        const float* __restrict__ inv_freq, ConvGeometry g, int write_kv) {
+    pdl_trigger();
+    pdl_wait();                                   // the projected rows and the step's metadata come from kernels in front
     const int row = blockIdx.x;
     const int slot_index = blockIdx.y * blockDim.x + threadIdx.x;
     const int total_pairs = g.q_pairs + g.k_pairs + g.v_pairs;
@@ -165,6 +167,8 @@ conv_rope_cache_packets_kernel(const T* __restrict__ proj, int64_t proj_stride, 
                                const int* __restrict__ block_table, int bt_stride, const float* __restrict__ inv_freq,
                                ConvGeometry g, int write_kv, int rows) {
     constexpr int N = Packet<T>::N;
+    pdl_trigger();
+    pdl_wait();                                   // the projected rows and the step's metadata come from kernels in front
     const int packet = blockIdx.y * blockDim.x + threadIdx.x;
     if (packet >= g.channels / N) return;
     const int c0 = packet * N;
@@ -260,6 +264,8 @@ template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ proj, int64_t proj_stride, float* __restrict__ state,
                                          const int* __restrict__ row_start, const int* __restrict__ seq_begin,
                                          const int* __restrict__ state_slots, int channels, int J) {
+    pdl_trigger();
+    pdl_wait();                                   // the convolution in front still reads the old state
     const int seq = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= channels) return;
@@ -304,7 +310,10 @@ int launch(const void* proj, int64_t proj_stride, const float* taps, float* stat
     if (g.dim % N == 0 && g.vdim % N == 0 && g.taps <= 4 && proj_stride % N == 0 && q_stride % N == 0 &&
         bits % 16 == 0) {
         const dim3 tiles((rows + kRowTile - 1) / kRowTile, (g.channels / N + 127) / 128);
-#define TB_CONV(S, J)                                                                                                    conv_rope_cache_packets_kernel<T, S, J><<<tiles, 128, 0, stream>>>(                                                      (const T*)proj, proj_stride, taps, state, (T*)q_out, q_stride, (T*)cache, positions, seq_of_row, row_start,           seq_begin, state_slots, block_table, bt_stride, inv_freq, g, write_kv, rows)
+#define TB_CONV(S, J)                                                                                             \
+    tb_launch_pdl(conv_rope_cache_packets_kernel<T, S, J>, tiles, dim3(128), 0, stream, (const T*)proj,           \
+                  proj_stride, taps, state, (T*)q_out, q_stride, (T*)cache, positions, seq_of_row, row_start,     \
+                  seq_begin, state_slots, block_table, bt_stride, inv_freq, g, write_kv, rows)
         if (single) {
             if (g.taps == 1) TB_CONV(true, 1); else if (g.taps == 2) TB_CONV(true, 2);
             else if (g.taps == 3) TB_CONV(true, 3); else TB_CONV(true, 4);
@@ -318,13 +327,13 @@ int launch(const void* proj, int64_t proj_stride, const float* taps, float* stat
     const int total = g.q_pairs + g.k_pairs + g.v_pairs;
     const dim3 grid(rows, (total + 127) / 128);
     if (single)
-        conv_rope_cache_kernel<T, true><<<grid, 128, 0, stream>>>(
-            (const T*)proj, proj_stride, taps, state, (T*)q_out, q_stride, (T*)cache, positions, seq_of_row, row_start,
-            seq_begin, state_slots, block_table, bt_stride, inv_freq, g, write_kv);
+        tb_launch_pdl(conv_rope_cache_kernel<T, true>, grid, dim3(128), 0, stream, (const T*)proj, proj_stride, taps,
+                      state, (T*)q_out, q_stride, (T*)cache, positions, seq_of_row, row_start, seq_begin, state_slots,
+                      block_table, bt_stride, inv_freq, g, write_kv);
     else
-        conv_rope_cache_kernel<T, false><<<grid, 128, 0, stream>>>(
-            (const T*)proj, proj_stride, taps, state, (T*)q_out, q_stride, (T*)cache, positions, seq_of_row, row_start,
-            seq_begin, state_slots, block_table, bt_stride, inv_freq, g, write_kv);
+        tb_launch_pdl(conv_rope_cache_kernel<T, false>, grid, dim3(128), 0, stream, (const T*)proj, proj_stride, taps,
+                      state, (T*)q_out, q_stride, (T*)cache, positions, seq_of_row, row_start, seq_begin, state_slots,
+                      block_table, bt_stride, inv_freq, g, write_kv);
     return tb_launch_status();
 }
 
@@ -363,12 +372,11 @@ TB_EXPORT int tb_conv_state_update(const void* proj, int64_t proj_stride, float*
     if (taps_count > kMaxTaps) return TB_ERR_BAD_SIZE;
     const dim3 grid(num_seqs, (channels + 127) / 128);
     if (dtype == TB_F32)
-        conv_state_update_kernel<float><<<grid, 128, 0, stream>>>((const float*)proj, proj_stride, state, row_start,
-                                                                  seq_begin, state_slots, channels, taps_count);
+        tb_launch_pdl(conv_state_update_kernel<float>, grid, dim3(128), 0, stream, (const float*)proj, proj_stride, state,
+                      row_start, seq_begin, state_slots, channels, taps_count);
     else if (dtype == TB_BF16)
-        conv_state_update_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)proj, proj_stride, state,
-                                                                          row_start, seq_begin, state_slots, channels,
-                                                                          taps_count);
+        tb_launch_pdl(conv_state_update_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)proj,
+                      proj_stride, state, row_start, seq_begin, state_slots, channels, taps_count);
     else
         return TB_ERR_BAD_DTYPE;
     return tb_launch_status();

@@ -31,6 +31,8 @@ gated_recurrence_kernel(const TI* __restrict__ proj, int64_t proj_stride, const 
                         int64_t out_stride, const int* __restrict__ row_start, const int* __restrict__ state_slots,
                         int width) {
     __shared__ float run_a[kMaxRuns][kChannels], run_b[kMaxRuns][kChannels];
+    pdl_trigger();
+    pdl_wait();                                   // the projections and the row starts come from kernels in front
     const int ch = threadIdx.x % kChannels, run = threadIdx.x / kChannels, runs = blockDim.x / kChannels;
     const int seq = blockIdx.x;
     const int c = blockIdx.y * kChannels + ch;
@@ -84,10 +86,10 @@ int launch(const void* proj, int64_t proj_stride, const float* bias_z, const flo
     int runs = 2;                                                       // (a block is at least one warp)
     while (runs < kMaxRuns && runs * 16 < max_new) runs <<= 1;          // runs of at least 16 rows
     const dim3 grid(num_seqs, (width + kChannels - 1) / kChannels);
-    gated_recurrence_kernel<TI, TO><<<grid, runs * kChannels, 0, stream>>>((const TI*)proj, proj_stride, bias_z, bias_x,
-                                                                          state, (TO*)out, out_stride, row_start,
-                                                                          state_slots, width);
-    return tb_launch_status();
+    cudaError_t launched = tb_launch_pdl(gated_recurrence_kernel<TI, TO>, grid, dim3(runs * kChannels), 0, stream,
+                                         (const TI*)proj, proj_stride, bias_z, bias_x, state, (TO*)out, out_stride,
+                                         row_start, state_slots, width);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
 }  // namespace

@@ -185,6 +185,8 @@ __global__ void group_rms_norm_kernel(const float* __restrict__ res, const U* __
                                       int part, int groups, float eps) {
     extern __shared__ __align__(16) float part_cache[];
     __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();                                   // the stream and its update come from kernels in front
     const int64_t base = (int64_t)blockIdx.x * part;
     const float* wp = w + (int64_t)(blockIdx.x % groups) * part;
     float ss = 0.0f;
@@ -231,6 +233,8 @@ group_rms_norm4_kernel(const float* __restrict__ res, const U* __restrict__ upd,
                        T* __restrict__ y, float* __restrict__ res_out, int part, int groups, float eps) {
     extern __shared__ __align__(16) float part_cache[];
     __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();                                   // the stream and its update come from kernels in front
     const int64_t base = (int64_t)blockIdx.x * part;
     const float* wp = w + (int64_t)(blockIdx.x % groups) * part;
     float ss = 0.0f;
@@ -275,22 +279,22 @@ int launch_group(const float* res, const void* upd, const float* w, void* y, flo
         if (upd != nullptr) {
             auto kernel = group_rms_norm4_kernel<U, T, true>;
             if (smem > 40 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            kernel<<<grid, threads4, smem, stream>>>(res, (const U*)upd, w, (T*)y, res_out, part, groups, eps);
+            tb_launch_pdl(kernel, grid, dim3(threads4), smem, stream, res, (const U*)upd, w, (T*)y, res_out, part, groups, eps);
         } else {
             auto kernel = group_rms_norm4_kernel<U, T, false>;
             if (smem > 40 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            kernel<<<grid, threads4, smem, stream>>>(res, nullptr, w, (T*)y, nullptr, part, groups, eps);
+            tb_launch_pdl(kernel, grid, dim3(threads4), smem, stream, res, (const U*)nullptr, w, (T*)y, (float*)nullptr, part, groups, eps);
         }
         return tb_launch_status();
     }
     if (upd != nullptr) {
         auto kernel = group_rms_norm_kernel<U, T, true>;
         if (smem > 40 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kernel<<<grid, threads, smem, stream>>>(res, (const U*)upd, w, (T*)y, res_out, part, groups, eps);
+        tb_launch_pdl(kernel, grid, dim3(threads), smem, stream, res, (const U*)upd, w, (T*)y, res_out, part, groups, eps);
     } else {
         auto kernel = group_rms_norm_kernel<U, T, false>;
         if (smem > 40 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kernel<<<grid, threads, smem, stream>>>(res, nullptr, w, (T*)y, nullptr, part, groups, eps);
+        tb_launch_pdl(kernel, grid, dim3(threads), smem, stream, res, (const U*)nullptr, w, (T*)y, (float*)nullptr, part, groups, eps);
     }
     return tb_launch_status();
 }

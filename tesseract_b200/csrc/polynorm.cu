@@ -35,6 +35,8 @@ __global__ void polynorm_kernel(const T* z, int64_t z_stride, const float* __res
     extern __shared__ __align__(16) float row_cache[];
     __shared__ float scratch[3][32];
     constexpr int N = Packet<T>::N;
+    pdl_trigger();
+    pdl_wait();                                   // the rows come from the product in front
     const T* zr = z + (int64_t)blockIdx.x * z_stride;
     float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
     if (VEC) {
@@ -99,8 +101,9 @@ int launch_kind(const void* z, int64_t z_stride, const float* coefficients, void
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
     }
-    kernel<<<rows, threads, smem, stream>>>((const T*)z, z_stride, coefficients, (T*)y, y_stride, width, eps);
-    return tb_launch_status();
+    cudaError_t launched = tb_launch_pdl(kernel, dim3(rows), dim3(threads), smem, stream, (const T*)z, z_stride,
+                                         coefficients, (T*)y, y_stride, width, eps);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
 template <typename T>
