@@ -476,3 +476,33 @@ def test_replay_program_runs_a_revesun_folder(folders, tmp_path):
     scale = float(np.abs(want).max())
     assert np.abs(first - want[[0, 19]]).max() <= 2e-5 * scale
     assert np.abs(second - want[[29]]).max() <= 2e-5 * scale
+
+
+def test_command_line_generates_and_prints_the_plan(folders):
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder = folders("p")
+    common = [sys.executable, os.path.join(root, "bin", "tesseract"), "--model-path", folder, "--kv-capacity-tokens",
+              "256", "--max-running", "2", "--dtype", "float32"]
+    done = subprocess.run(common + ["--prompt-ids", "5,6,7,8", "--random-prompt", "11", "--max-tokens", "4",
+                                    "--temperature", "0", "--ignore-eos", "--json", "--check-weights"],
+                          capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert "weights checked: final.norm" in done.stderr
+    records = [json.loads(line) for line in done.stdout.strip().splitlines()]
+    assert len(records) == 2 and all(len(r["token_ids"]) == 4 and r["finish_reason"] == "length" for r in records)
+    config, tensors = plain.load_folder(folder)
+    tokens = [5, 6, 7, 8]
+    for got in records[0]["token_ids"]:
+        logits = plain.forward(config, tensors, tokens)[-1].numpy()
+        best = int(np.argmax(logits))
+        assert got == best or float(logits[best] - logits[got]) <= GREEDY_MARGIN["float32"] * float(np.abs(logits).max())
+        tokens.append(got)
+    shown = subprocess.run(common + ["--print-plan"], capture_output=True, text=True, timeout=600)
+    assert shown.returncode == 0, shown.stderr[-2000:]
+    assert "kernel plan for Revesun" in shown.stdout
+    assert "mixer 'conv_attention'" in shown.stdout and "mixer 'mingru'" in shown.stdout
