@@ -167,6 +167,7 @@ conv_rope_cache_packets_kernel(const T* __restrict__ proj, int64_t proj_stride, 
                                const int* __restrict__ block_table, int bt_stride, const float* __restrict__ inv_freq,
                                ConvGeometry g, int write_kv, int rows) {
     constexpr int N = Packet<T>::N;
+    constexpr int ROWS = SINGLE ? 1 : kRowTile;      // (a step of single rows has few of them: a thread a row)
     pdl_trigger();
     pdl_wait();                                   // the projected rows and the step's metadata come from kernels in front
     const int packet = blockIdx.y * blockDim.x + threadIdx.x;
@@ -188,10 +189,10 @@ conv_rope_cache_packets_kernel(const T* __restrict__ proj, int64_t proj_stride, 
     const int64_t page_elems = (int64_t)g.kv_heads * g.page_size * (g.dim + g.vdim);
 
     // what the rows of the tile are, asked for at once (each is a chain of two or three dependent loads)
-    int row_pos[kRowTile], row_begin[kRowTile], row_first[kRowTile], row_slot[kRowTile], row_page[kRowTile];
+    int row_pos[ROWS], row_begin[ROWS], row_first[ROWS], row_slot[ROWS], row_page[ROWS];
 #pragma unroll
-    for (int r = 0; r < kRowTile; ++r) {
-        const int row = min(blockIdx.x * kRowTile + r, rows - 1);
+    for (int r = 0; r < ROWS; ++r) {
+        const int row = min(blockIdx.x * ROWS + r, rows - 1);
         const int seq = seq_of_row[row];
         row_pos[r] = positions[row];
         row_begin[r] = seq_begin[seq];
@@ -200,8 +201,8 @@ conv_rope_cache_packets_kernel(const T* __restrict__ proj, int64_t proj_stride, 
         row_page[r] = (segment != 0 && write_kv) ? block_table[(int64_t)seq * bt_stride + row_pos[r] / g.page_size] : 0;
     }
 #pragma unroll
-    for (int r = 0; r < kRowTile; ++r) {
-        const int row = blockIdx.x * kRowTile + r;
+    for (int r = 0; r < ROWS; ++r) {
+        const int row = blockIdx.x * ROWS + r;
         if (row >= rows) return;
         const int pos = row_pos[r];
         const int begin = row_begin[r];
@@ -309,7 +310,8 @@ int launch(const void* proj, int64_t proj_stride, const float* taps, float* stat
     const uintptr_t bits = (uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)state | (uintptr_t)taps;
     if (g.dim % N == 0 && g.vdim % N == 0 && g.taps <= 4 && proj_stride % N == 0 && q_stride % N == 0 &&
         bits % 16 == 0) {
-        const dim3 tiles((rows + kRowTile - 1) / kRowTile, (g.channels / N + 127) / 128);
+        const int tile = single ? 1 : kRowTile;
+        const dim3 tiles((rows + tile - 1) / tile, (g.channels / N + 127) / 128);
 #define TB_CONV(S, J)                                                                                             \
     tb_launch_pdl(conv_rope_cache_packets_kernel<T, S, J>, tiles, dim3(128), 0, stream, (const T*)proj,           \
                   proj_stride, taps, state, (T*)q_out, q_stride, (T*)cache, positions, seq_of_row, row_start,     \

@@ -7,7 +7,8 @@
 //
 // Everything but the projections is 32-bit.  A block owns 16 neighbouring channels of one sequence (a half-warp of
 // lanes, so rows are read in whole 64-byte pieces) and cuts the sequence's rows of this step into one run per
-// half-warp, up to 64 runs: a prompt of one sequence still fills the machine.  Because S_t is affine in S_(t-1), a
+// half-warp, up to 64 runs: a prompt of one sequence still fills the machine (in steps of at most 16 rows a
+// sequence a block owns 128 channels and one run).  Because S_t is affine in S_(t-1), a
 // run is first reduced to the pair (A, B) with S_end = A * S_start + B (A the product of the (1 - z), B the run from
 // a zero start); the runs' pairs are chained from the slot's state to give every run its start, and the run is then
 // walked again with that start, writing y.  A sequence whose rows fit one run (a decoded row, a short portion) is
@@ -17,8 +18,9 @@
 
 namespace {
 
-constexpr int kChannels = 16;       // channels of a block
+constexpr int kChannels = 16;       // channels of a block that cuts its rows into runs
 constexpr int kMaxRuns = 64;        // runs of rows of a block (threads = runs * channels)
+constexpr int kWideChannels = 128;  // channels of a block in steps of few rows (one run: the plain walk)
 
 // (the exponential and the division as single hardware approximations: two units in the last place each, far inside
 // what a 32-bit result is asked to hold)
@@ -29,13 +31,13 @@ __global__ void __launch_bounds__(kMaxRuns * kChannels)
 gated_recurrence_kernel(const TI* __restrict__ proj, int64_t proj_stride, const float* __restrict__ bias_z,
                         const float* __restrict__ bias_x, float* __restrict__ state, TO* __restrict__ out,
                         int64_t out_stride, const int* __restrict__ row_start, const int* __restrict__ state_slots,
-                        int width) {
-    __shared__ float run_a[kMaxRuns][kChannels], run_b[kMaxRuns][kChannels];
+                        int width, int chans) {
+    __shared__ float run_a[kMaxRuns * kChannels], run_b[kMaxRuns * kChannels];
     pdl_trigger();
     pdl_wait();                                   // the projections and the row starts come from kernels in front
-    const int ch = threadIdx.x % kChannels, run = threadIdx.x / kChannels, runs = blockDim.x / kChannels;
+    const int ch = threadIdx.x % chans, run = threadIdx.x / chans, runs = blockDim.x / chans;
     const int seq = blockIdx.x;
-    const int c = blockIdx.y * kChannels + ch;
+    const int c = blockIdx.y * chans + ch;
     const bool active = c < width;
     const int first_row = row_start[seq];
     const int n = row_start[seq + 1] - first_row;
@@ -60,10 +62,10 @@ gated_recurrence_kernel(const TI* __restrict__ proj, int64_t proj_stride, const 
                 b = fmaf(z, cand, keep * b);
             }
         }
-        run_a[run][ch] = a;
-        run_b[run][ch] = b;
+        run_a[run * chans + ch] = a;
+        run_b[run * chans + ch] = b;
         __syncthreads();
-        for (int k = 0; k < run; ++k) s = fmaf(run_a[k][ch], s, run_b[k][ch]);
+        for (int k = 0; k < run; ++k) s = fmaf(run_a[k * chans + ch], s, run_b[k * chans + ch]);
     }
     if (!active) return;
 #pragma unroll 4
@@ -83,12 +85,13 @@ template <typename TI, typename TO>
 int launch(const void* proj, int64_t proj_stride, const float* bias_z, const float* bias_x, float* state, void* out,
            int64_t out_stride, const int* row_start, const int* state_slots, int num_seqs, int width, int max_new,
            cudaStream_t stream) {
-    int runs = 2;                                                       // (a block is at least one warp)
+    int runs = 1;
     while (runs < kMaxRuns && runs * 16 < max_new) runs <<= 1;          // runs of at least 16 rows
-    const dim3 grid(num_seqs, (width + kChannels - 1) / kChannels);
-    cudaError_t launched = tb_launch_pdl(gated_recurrence_kernel<TI, TO>, grid, dim3(runs * kChannels), 0, stream,
+    const int chans = runs == 1 ? kWideChannels : kChannels;
+    const dim3 grid(num_seqs, (width + chans - 1) / chans);
+    cudaError_t launched = tb_launch_pdl(gated_recurrence_kernel<TI, TO>, grid, dim3(runs * chans), 0, stream,
                                          (const TI*)proj, proj_stride, bias_z, bias_x, state, (TO*)out, out_stride,
-                                         row_start, state_slots, width);
+                                         row_start, state_slots, width, chans);
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
@@ -102,7 +105,7 @@ TB_EXPORT int tb_gated_recurrence(const void* proj, int64_t proj_stride, int in_
                                   const int* row_start, const int* state_slots, int num_seqs, int width, int max_new,
                                   cudaStream_t stream) {
     if (num_seqs == 0) return 0;
-    if (width < 1 || (width + kChannels - 1) / kChannels > 65535) return TB_ERR_BAD_SIZE;
+    if (width < 1 || (width + kChannels - 1) / kChannels > 65535) return TB_ERR_BAD_SIZE;      // (grid.y)
     if (in_dtype == TB_F32 && out_dtype == TB_F32)
         return launch<float, float>(proj, proj_stride, bias_z, bias_x, state, out, out_stride, row_start, state_slots,
                                     num_seqs, width, max_new, stream);

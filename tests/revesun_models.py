@@ -29,4 +29,7 @@ TINY_REVESUN = {
     "r": {"architecture": "Revesun", "width": 32, "vocab": 77, "norm": {"eps": 1e-4, "groups": 4},
           "layers": [attention(1, 1, 24, 16, 4, 1000, 24, 30.0, 0.15, None),
                      mingru(64, 48)]},
+    # recurrent layers only: a model without a single page
+    "s": {"architecture": "Revesun", "width": 40, "vocab": 64, "norm": {"eps": 1e-5, "groups": 2},
+          "layers": [mingru(24, None), mingru(56, 32)]},
 }

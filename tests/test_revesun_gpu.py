@@ -272,7 +272,7 @@ def test_gated_recurrence_carries_its_state(width, in_dtype, out_dtype):
 # ----------------------------------------------------------------------------- whole models
 
 
-LENGTHS = {"p": [1, 2, 3, 14, 40, 97], "q": [5, 33, 66, 130], "r": [4, 27, 81]}
+LENGTHS = {"p": [1, 2, 3, 14, 40, 97], "q": [5, 33, 66, 130], "r": [4, 27, 81], "s": [1, 9, 70]}
 
 
 def make_requests(name):
@@ -326,7 +326,7 @@ def plains(folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["p", "q", "r"])
+@pytest.mark.parametrize("name", ["p", "q", "r", "s"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "portions", "twos"])
 def test_cuts_match_plain(engines, plains, name, dtype, cut):
     """Whole prompts, prompts with a decoded tail (which crosses block edges), portions of changing size, and portions
@@ -340,6 +340,20 @@ def test_cuts_match_plain(engines, plains, name, dtype, cut):
     compare(replay(stepper, steps), plains(name), REL[dtype], f"{name}/{dtype}/{cut}")
     stepper.cache.check()
     assert stepper.cache.used_pages() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_model_without_pages_in_mixed_batches_and_generation(engines, plains, folders, dtype):
+    from tesseract_b200 import LLM, SamplingParams
+
+    requests = make_requests("s")
+    requests.update({f"sx{i}": random_tokens(TINY_REVESUN["s"]["vocab"], n, seed=40 + i) for i, n in enumerate([31, 12, 50])})
+    steps = trace_mixed(requests, seed=9, live_max=3)
+    stepper = engines("s", dtype, capacity_tokens=max_live_tokens(steps), max_requests=3)
+    compare(replay(stepper, steps), plains("s", requests), REL[dtype], f"s/{dtype}/mixed")
+    llm = LLM(folders("s"), dtype=dtype, kv_capacity_tokens=256, max_running=2, prefill_chunk_tokens=32)
+    outs = llm.generate([[1, 2, 3], [4] * 40], SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True))
+    assert [len(o.token_ids) for o in outs] == [5, 5]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
