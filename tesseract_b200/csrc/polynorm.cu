@@ -44,8 +44,10 @@ __global__ void polynorm_kernel(const T* z, int64_t z_stride, const float* __res
             float v[N];
             Packet<T>::load(zr + j, v);
 #pragma unroll
+            for (int e = 0; e < N; e += 4)              // (four numbers a store: a quarter of the bank conflicts)
+                *reinterpret_cast<float4*>(row_cache + j + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+#pragma unroll
             for (int e = 0; e < N; ++e) {
-                row_cache[j + e] = v[e];
                 const float v2 = v[e] * v[e], v3 = v2 * v[e];
                 s1 = fmaf(v[e], v[e], s1);
                 s2 = fmaf(v2, v2, s2);
@@ -73,8 +75,13 @@ __global__ void polynorm_kernel(const T* z, int64_t z_stride, const float* __res
         for (int j = threadIdx.x * N; j < width; j += blockDim.x * N) {      // each thread rereads what it wrote
             float o[N];
 #pragma unroll
+            for (int e = 0; e < N; e += 4) {
+                const float4 t = *reinterpret_cast<const float4*>(row_cache + j + e);
+                o[e] = t.x; o[e + 1] = t.y; o[e + 2] = t.z; o[e + 3] = t.w;
+            }
+#pragma unroll
             for (int e = 0; e < N; ++e) {
-                const float v = row_cache[j + e];
+                const float v = o[e];
                 const float v2 = v * v;
                 o[e] = k1 * v + k2 * v2 + k3 * (v2 * v) + k0;
             }
