@@ -110,6 +110,12 @@ class ConvAttention(Mixer):
             return torch.randn(shape, generator=generator, dtype=torch.float32) * 0.5
         return torch.randn(shape, generator=generator, dtype=torch.float32) * (shape[-1] ** -0.5)
 
+    def products(self):
+        """``(name, Linear, epilogue)`` of the mixer's matrix products, for the printed kernel plan."""
+        from .. import plan
+
+        return [("q/k/v/gate", self.in_proj, plan.BF16), ("o", self.o_proj, plan.F32 if self.stream_f32 else plan.BF16)]
+
     def cache_need(self):
         pages = PagedKeyValueNeed(num_kv_heads=self.num_kv_heads, key_dim=self.key_dim, value_dim=self.value_dim,
                                   window=self.mask_size if self.mask_kind == "window" else None,
@@ -124,6 +130,9 @@ class ConvAttention(Mixer):
         pages, state = (cache if isinstance(cache, tuple) else (cache, None))
         if pages is None or pages.storage is None:
             raise RuntimeError("conv_attention needs a paged key/value cache binding")
+        if not pages.writes:
+            raise NotImplementedError("conv_attention keeps a cache and a convolution state of its own: a run entry "
+                                      "cannot read another entry's")
         group = ctx.groups[pages.group]
         proj = self.in_proj.forward(x)
         rows = proj.shape[0]

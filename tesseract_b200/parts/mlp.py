@@ -109,6 +109,10 @@ class PolyNormMLP(FeedForward):
             return torch.tensor([0.6, 0.3, 0.2, 0.05]) + torch.randn(shape, generator=generator) * 0.05
         return torch.randn(shape, generator=generator, dtype=torch.float32) * (shape[-1] ** -0.5)
 
+    def products(self):
+        """``(name, Linear, epilogue)`` of the feed-forward's matrix products, for the printed kernel plan."""
+        return [("up", self.up_proj, plan.BF16), ("down", self.down_proj, plan.F32 if self.stream_f32 else plan.BF16)]
+
     def forward(self, x, ctx: StepContext, follow=None):
         if isinstance(x, DeferredNorm):
             x = x.materialize()

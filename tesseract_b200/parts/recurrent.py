@@ -58,6 +58,12 @@ class MinGRU(Mixer):
             return torch.randn(shape, generator=generator, dtype=torch.float32) * 0.5
         return torch.randn(shape, generator=generator, dtype=torch.float32) * (shape[-1] ** -0.5)
 
+    def products(self):
+        """``(name, Linear, epilogue)`` of the mixer's matrix products, for the printed kernel plan."""
+        from .. import plan
+
+        return [("z/x/gate", self.in_proj, plan.F32), ("o", self.o_proj, plan.F32 if self.stream_f32 else plan.BF16)]
+
     def cache_need(self) -> StateNeed:
         return StateNeed((self.width,), torch.float32)
 

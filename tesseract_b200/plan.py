@@ -284,6 +284,10 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
                 o = mixer.o_proj
                 o_plan = product(dtype, rows, o.out_features, o.in_features, follow=True)
                 lines.append(f"    o        {o_plan}")
+            elif hasattr(mixer, "products"):
+                lines.append(f"    mixer    '{mixer.kind}' (its own kernels between the products)")
+                for name, linear, epilogue in mixer.products():
+                    lines.append(f"      {name:10s} {product(dtype, rows, linear.out_features, linear.in_features, epilogue=epilogue)}")
             else:
                 lines.append(f"    mixer    '{mixer.kind}' (its own code)")
             if isinstance(ffn, SwiGLU):
@@ -292,6 +296,10 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
                 prepared = isinstance(mixer, Attention) and o_plan.prepares_norm
                 lines.append(f"    gate/up  {product(dtype, rows, gu.out_features, gu.in_features, epilogue=epilogue, norm='prepared' if prepared else 'add_norm')}")
                 lines.append(f"    down     {product(dtype, rows, down.out_features, down.in_features, follow=True)}")
+            elif ffn is not None and hasattr(ffn, "products"):
+                lines.append(f"    feed-forward '{ffn.kind}' (its own kernel between the products)")
+                for name, linear, epilogue in ffn.products():
+                    lines.append(f"      {name:10s} {product(dtype, rows, linear.out_features, linear.in_features, epilogue=epilogue)}")
             elif ffn is not None:
                 lines.append(f"    feed-forward '{ffn.kind}' (its own code)")
     proj = getattr(model.head, "proj", None)
