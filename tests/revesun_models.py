@@ -33,3 +33,28 @@ TINY_REVESUN = {
     "s": {"architecture": "Revesun", "width": 40, "vocab": 64, "norm": {"eps": 1e-5, "groups": 2},
           "layers": [mingru(24, None), mingru(56, 32)]},
 }
+
+
+def random_config(seed: int) -> dict:
+    """A Revesun configuration drawn from ``seed``: two to five layers of either kind in any order, with or without
+    a feed-forward, sizes that are and are not multiples of eight, one to six taps, blocks from 3 to 500 positions."""
+    import random
+
+    r = random.Random(seed)
+    width = r.choice([24, 40, 64, 66, 96, 136, 200, 256, 320])
+    groups = r.choice([g for g in range(1, 9) if width % g == 0])
+    layers = []
+    for _ in range(r.randint(2, 5)):
+        ff = r.choice([None, r.choice([8, 40, 100, 256, 513])])
+        if r.random() < 0.6:
+            heads = r.choice([1, 2, 3, 4, 6, 8])
+            kv_heads = r.choice([d for d in range(1, heads + 1) if heads % d == 0])
+            dim = r.choice([6, 8, 12, 16, 24, 32, 40, 64, 96, 128])
+            vdim = r.choice([4, 8, 10, 16, 24, 48, 64, 96, 160, 256])
+            layers.append(attention(heads, kv_heads, dim, vdim, r.randint(1, 6), r.choice([3, 16, 17, 50, 64, 120, 500]),
+                                    r.choice(range(0, dim + 1, 2)), r.choice([10.0, 1000.0, 50000.0]),
+                                    r.choice([dim ** -0.5, 0.3, 0.07]), ff))
+        else:
+            layers.append(mingru(r.choice([8, 30, 64, 100, 257]), ff))
+    return {"architecture": "Revesun", "width": width, "vocab": r.randint(40, 700),
+            "norm": {"eps": r.choice([1e-5, 1e-6]), "groups": groups}, "layers": layers}

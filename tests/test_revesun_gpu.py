@@ -520,3 +520,29 @@ def test_command_line_generates_and_prints_the_plan(folders):
     assert shown.returncode == 0, shown.stderr[-2000:]
     assert "kernel plan for Revesun" in shown.stdout
     assert "mixer 'conv_attention'" in shown.stdout and "mixer 'mingru'" in shown.stdout
+
+
+@pytest.mark.parametrize("seed", [3, 10, 14, 54, 113, 137])
+def test_random_configurations_match_plain_in_float32(tmp_path, seed):
+    """Configurations drawn at random (layer kinds, order, every size and constant), each whole, with a decoded tail,
+    in portions and in mixed batches.  In 32-bit only: a norm over a group of three numbers magnifies bfloat16's
+    rounding without bound, whatever computes it."""
+    import random
+
+    from tesseract_b200.engine import load_model, make_stepper
+    from tesseract_b200.weights.random_init import write_random_model
+    from tests.revesun_models import random_config
+
+    config = random_config(seed)
+    folder = write_random_model(str(tmp_path / "model"), config, seed=seed)
+    loaded, tensors = plain.load_folder(folder)
+    r = random.Random(seed + 1000)
+    lengths = [1, r.randint(2, 40), r.randint(41, 140), r.randint(141, 300), r.randint(5, 90)]
+    requests = {f"q{i}": random_tokens(config["vocab"], n, seed=seed * 10 + i) for i, n in enumerate(lengths)}
+    want = {rid: plain.forward(loaded, tensors, tokens).numpy() for rid, tokens in requests.items()}
+    model = load_model(folder, dtype="float32")
+    for name, steps in (("whole", trace_whole(requests)), ("tail", trace_tail(requests, tail=20)),
+                        ("portions", trace_portions(requests)), ("mixed", trace_mixed(requests, seed=seed, live_max=4))):
+        stepper = make_stepper(model, capacity_tokens=max(1024, max_live_tokens(steps)), max_requests=4)
+        compare(replay(stepper, steps), want, 3e-5, f"seed {seed}/{name}")
+        assert stepper.cache.used_pages() == 0
