@@ -405,7 +405,8 @@ int launch_vec(const void* q, int64_t q_stride, const void* gate, int64_t gate_s
     else if (vdim <= 96) TB_LAUNCH(3);
     else if (vdim <= 128) TB_LAUNCH(4);
     else if (vdim <= 192) TB_LAUNCH(6);
-    else TB_LAUNCH(8);
+    else if (vdim <= 256) TB_LAUNCH(8);
+    else TB_LAUNCH(16);
 #undef TB_LAUNCH
     return tb_launch_status();
 }
@@ -443,7 +444,7 @@ TB_EXPORT int tb_attention_masked(const void* q, int64_t q_stride, const void* g
                                   int vdim, int page_size, int mask_kind, int mask_size, int sink, float scale,
                                   int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
-    if (dim < 1 || dim > 1024 || vdim < 1 || vdim > 256) return TB_ERR_BAD_SIZE;
+    if (dim < 1 || dim > 1024 || vdim < 1 || vdim > 512) return TB_ERR_BAD_SIZE;
     if (kv_heads < 1 || heads < 1 || heads % kv_heads != 0 || page_size < 1) return TB_ERR_BAD_SIZE;
     if (mask_kind < MASK_CAUSAL || mask_kind > MASK_BLOCKS) return TB_ERR_BAD_SIZE;
     if (mask_kind != MASK_CAUSAL && mask_size < 1) return TB_ERR_BAD_SIZE;

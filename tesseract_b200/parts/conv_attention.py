@@ -66,8 +66,8 @@ class ConvAttention(Mixer):
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if not 1 <= self.taps <= 8:
             raise ValueError(f"the short convolution takes 1 to 8 taps, got {self.taps}")
-        if not (1 <= self.key_dim <= 1024 and 1 <= self.value_dim <= 256):
-            raise ValueError("the attention kernel takes keys of up to 1024 and values of up to 256 numbers a head")
+        if not (1 <= self.key_dim <= 1024 and 1 <= self.value_dim <= 512):
+            raise ValueError("the attention kernel takes keys of up to 1024 and values of up to 512 numbers a head")
         self.q_width = self.num_heads * self.key_dim
         self.k_width = self.num_kv_heads * self.key_dim
         self.v_width = self.num_kv_heads * self.value_dim

@@ -101,7 +101,8 @@ def _plain_mask(T, kind, size):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,d,dv", [(4, 2, 16, 24), (3, 3, 20, 12), (6, 1, 40, 8), (2, 1, 128, 128),
-                                                 (8, 2, 64, 32), (6, 2, 32, 16), (5, 1, 8, 8)])
+                                                 (8, 2, 64, 32), (6, 2, 32, 16), (5, 1, 8, 8), (2, 1, 16, 320),
+                                                 (1, 1, 520, 8)])
 @pytest.mark.parametrize("kind,size", [("blocks", 300), ("blocks", 16), ("blocks", 7), ("window", 33), ("causal", 0)])
 @pytest.mark.parametrize("sink,gated", [(True, True), (False, False)])
 def test_masked_attention_sees_exactly_its_keys(dtype, heads, kv_heads, d, dv, kind, size, sink, gated):
