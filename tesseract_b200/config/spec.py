@@ -10,8 +10,10 @@ in the part registries.  Nothing below this line knows an architecture's name.
 * A :class:`LayerSpec` is one block: its arrangement kind, mixer, feed-forward
   and norms.  Layers may differ from one another freely.
 * ``run_order`` is the list of :class:`RunEntry` that the step function walks.
-  An entry names a layer (so a layer may run twice) and, optionally, an earlier
-  entry whose cache it reads instead of keeping its own.
+  An entry names a layer (so a layer may run twice, each time with a cache of its
+  own) and, optionally, an earlier entry whose cache it reads instead of keeping its
+  own, and an injection (one of ``ModelSpec.injections``) that transforms the stream
+  right before the entry's layer runs.
 """
 
 from __future__ import annotations
@@ -81,6 +83,7 @@ class RunEntry:
 
     layer: int
     cache_of: Optional[int] = None
+    inject: Optional[int] = None        # index into ``ModelSpec.injections``: runs on the stream before this layer
 
 
 @dataclass(frozen=True)
@@ -96,6 +99,7 @@ class ModelSpec:
     head: PartSpec
     bos_token_id: int = 0
     eos_token_ids: Tuple[int, ...] = ()
+    injections: Tuple[PartSpec, ...] = ()
 
     def validate(self) -> None:
         if not self.run_order:
@@ -103,6 +107,8 @@ class ModelSpec:
         for index, entry in enumerate(self.run_order):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"run_order[{index}] names layer {entry.layer}, model has {len(self.layers)}")
+            if entry.inject is not None and not 0 <= entry.inject < len(self.injections):
+                raise ValueError(f"run_order[{index}] names injection {entry.inject}, model has {len(self.injections)}")
             if entry.cache_of is not None:
                 if not 0 <= entry.cache_of < index:
                     raise ValueError(f"run_order[{index}].cache_of must name an earlier entry")

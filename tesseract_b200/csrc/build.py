@@ -54,6 +54,10 @@ SOURCES: Dict[str, List[str]] = {
     "conv_rope_cache": [],
     "attention_masked": [],
     "gated_recurrence": [],
+    "parallel_norm": [],
+    "pointwise": [],
+    "rope_norm_cache": [],
+    "experts": [],
 }
 
 

@@ -1,0 +1,462 @@
+// A feed-forward made of many small experts of which every row takes a few: the router, the grouping of rows by
+// expert, the experts' products, and the weighted sum.
+//
+//   tb_route_topk      z = W_r h in 32-bit (a K-ordered slice per lane, then a fixed butterfly); the `top` largest
+//                      z of a row, largest first (the lowest index wins a tie), and the softmax over those alone.
+//   tb_expert_plan     rows * top assignments (row t, slot s -> assignment t * top + s) are grouped by their expert:
+//                      offsets[e] .. offsets[e + 1] of `order` name the assignments of expert e.
+//   tb_expert_linear   out[a, :] = act(W[expert(a)] in[source(a), :]) for every assignment a, a tile of one expert's
+//                      assignments per block; source(a) is a / top (the row itself: the first product of an expert)
+//                      or a (the second).  Every output number is one chain over K that does not depend on which
+//                      other assignments share its tile.
+//   tb_expert_combine  out[t, :] = [base[t, :] +] sum_s weight[t, s] * y[t * top + s, :], slots in order, 32-bit.
+//
+// Nothing here needs the host to know how many rows an expert received: grids are sized for the worst case and
+// blocks without work leave at once, so a step's launches depend on its row count alone.
+#include "common.cuh"
+
+
+namespace {
+
+// ----------------------------------------------------------------------------- router
+
+constexpr int kRouteWarps = 4;
+
+// R rows a warp: a weight is loaded once for all of them.  The arithmetic of a row is the same for every R.
+template <typename T, int R>
+__global__ void __launch_bounds__(kRouteWarps * 32)
+route_topk_kernel(const T* __restrict__ x, int64_t x_stride, const float* __restrict__ router, int* __restrict__ ids,
+                  float* __restrict__ weights, int rows, int width, int experts, int top) {
+    extern __shared__ __align__(16) float route_smem[];          // per warp: R rows of `width`, then R * experts logits
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = (blockIdx.x * kRouteWarps + warp) * R;
+    if (row0 >= rows) return;                                    // the whole warp leaves; no block-wide barrier below
+    float* xs = route_smem + (size_t)warp * R * (width + experts);
+    float* zs = xs + (size_t)R * width;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int row = min(row0 + r, rows - 1);
+        const T* xr = x + (int64_t)row * x_stride;
+        for (int i = lane; i < width; i += 32) xs[r * width + i] = Elem<T>::load(xr + i);
+    }
+    __syncwarp();
+    for (int e = 0; e < experts; ++e) {
+        const float* w = router + (int64_t)e * width;
+        float dot[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) dot[r] = 0.0f;
+        for (int i = lane; i < width; i += 32) {
+            const float wv = w[i];
+#pragma unroll
+            for (int r = 0; r < R; ++r) dot[r] = fmaf(xs[r * width + i], wv, dot[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float z = warp_sum(dot[r]);
+            if (lane == 0) zs[r * experts + e] = z;
+        }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int row = row0 + r;
+        if (row >= rows) break;
+        float* z = zs + r * experts;
+        float first = 0.0f, total = 0.0f;
+        for (int s = 0; s < top; ++s) {
+            float best = -INFINITY;
+            int where = 0x7fffffff;
+            for (int e = lane; e < experts; e += 32) {
+                const float v = z[e];
+                if (v > best) { best = v; where = e; }          // (ascending e: the lowest index of equal values stays)
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int ow = __shfl_xor_sync(0xffffffffu, where, o);
+                if (ob > best || (ob == best && ow < where)) { best = ob; where = ow; }
+            }
+            if (where == 0x7fffffff) where = 0;                  // (only if every logit is NaN or -inf)
+            if (s == 0) first = best;
+            const float p = expf(best - first);
+            total += p;
+            if (lane == 0) {
+                ids[(int64_t)row * top + s] = where;
+                weights[(int64_t)row * top + s] = p;
+                z[where] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        const float inv = 1.0f / total;
+        for (int s = lane; s < top; s += 32) weights[(int64_t)row * top + s] *= inv;     // (lane 0's stores above are visible: same warp, synced)
+    }
+}
+
+// ----------------------------------------------------------------------------- grouping
+
+__global__ void __launch_bounds__(1024)
+expert_plan_kernel(const int* __restrict__ ids, int assignments, int experts, int* __restrict__ offsets,
+                   int* __restrict__ order) {
+    extern __shared__ int plan_smem[];                           // counts[experts], cursor[experts]
+    pdl_trigger();
+    pdl_wait();
+    int* counts = plan_smem;
+    int* cursor = plan_smem + experts;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int a = threadIdx.x; a < assignments; a += blockDim.x) {
+        const int e = ids[a];
+        if (e >= 0 && e < experts) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < experts; ++e) {
+            offsets[e] = run;
+            cursor[e] = run;
+            run += counts[e];
+        }
+        offsets[experts] = run;
+    }
+    __syncthreads();
+    // (which of an expert's assignments comes first is left to the atomics: no result depends on it)
+    for (int a = threadIdx.x; a < assignments; a += blockDim.x) {
+        const int e = ids[a];
+        if (e >= 0 && e < experts) order[atomicAdd(&cursor[e], 1)] = a;
+    }
+}
+
+// ----------------------------------------------------------------------------- the experts' products
+
+enum ExpertEpilogue : int { EXP_PLAIN = 0, EXP_SQUARED_RELU = 1 };
+
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+
+// The tile of this block: which expert, and the first of its assignments.  Returns false when the block has none.
+__device__ __forceinline__ bool find_tile(const int* __restrict__ offsets, int experts, int tile, int tile_rows,
+                                          int& expert, int& first, int& count) {
+    for (int e = 0; e < experts; ++e) {
+        const int begin = offsets[e], n = offsets[e + 1] - begin;
+        const int tiles = (n + tile_rows - 1) / tile_rows;
+        if (tile < tiles) {
+            expert = e;
+            first = begin + tile * tile_rows;
+            count = min(tile_rows, n - tile * tile_rows);
+            return true;
+        }
+        tile -= tiles;
+    }
+    return false;
+}
+
+// Plain multiply-adds, operands widened to 32-bit: the true 32-bit product, and the fallback for sizes the tensor-core
+// kernel does not take.  Every output element is one K-ordered chain k = 0, 1, ..., K - 1.
+template <typename T, typename O, int EPI>
+__global__ void __launch_bounds__(256)
+expert_linear_kernel(const T* __restrict__ in, int64_t in_stride, const T* __restrict__ W, O* __restrict__ out,
+                     int64_t out_stride, const int* __restrict__ offsets, const int* __restrict__ order, int experts,
+                     int top_div, int N, int K) {
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    __shared__ int rows_of[BM];
+    pdl_trigger();
+    pdl_wait();
+    int expert, first, count;
+    if (!find_tile(offsets, experts, blockIdx.y, BM, expert, first, count)) return;
+    const int tid = threadIdx.x;
+    if (tid < BM) rows_of[tid] = tid < count ? order[first + tid] : -1;
+    __syncthreads();
+    const T* We = W + (int64_t)expert * N * K;
+    const int n0 = blockIdx.x * BN;
+    const int tx = tid % 16, ty = tid / 16;
+    const int load_row = tid / 4;
+    const int load_k = (tid % 4) * 4;
+    const int a_assign = rows_of[load_row];
+    const T* a_src = a_assign < 0 ? nullptr : in + (int64_t)(a_assign / top_div) * in_stride;
+    const int wn = n0 + load_row;
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        float a[4] = {0.f, 0.f, 0.f, 0.f}, w[4] = {0.f, 0.f, 0.f, 0.f};
+        const int kk = k0 + load_k;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (a_src != nullptr && kk + e < K) a[e] = Elem<T>::load(a_src + kk + e);
+            if (wn < N && kk + e < K) w[e] = Elem<T>::load(We + (int64_t)wn * K + kk + e);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            As[load_k + e][load_row] = a[e];
+            Ws[load_k + e][load_row] = w[e];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float ar[TM], wr[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) ar[i] = As[k][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) wr[j] = Ws[k][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(ar[i], wr[j], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int a = rows_of[ty * TM + i];
+        if (a < 0) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (EPI == EXP_SQUARED_RELU) {
+                v = fmaxf(v, 0.0f);
+                v *= v;
+            }
+            Elem<O>::store(out + (int64_t)a * out_stride + n, v);
+        }
+    }
+}
+
+// bfloat16 on the tensor cores (mma.sync m16n8k16, 32-bit accumulators): a block is 64 assignments of one expert by
+// 64 features, a warp 16 assignments by 64 features; K in steps of 32 through shared memory.  K a multiple of 32.
+constexpr int MK = 32, MPAD = 8;
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, const uint32_t* b) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <typename O, int EPI>
+__global__ void __launch_bounds__(128)
+expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ in, int64_t in_stride, const __nv_bfloat16* __restrict__ W,
+                         O* __restrict__ out, int64_t out_stride, const int* __restrict__ offsets,
+                         const int* __restrict__ order, int experts, int top_div, int N, int K) {
+    __shared__ __align__(16) __nv_bfloat16 As[BM][MK + MPAD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[BN][MK + MPAD];
+    __shared__ int rows_of[BM];
+    pdl_trigger();
+    pdl_wait();
+    int expert, first, count;
+    if (!find_tile(offsets, experts, blockIdx.y, BM, expert, first, count)) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < BM) rows_of[tid] = tid < count ? order[first + tid] : -1;
+    __syncthreads();
+    const __nv_bfloat16* We = W + (int64_t)expert * N * K;
+    const int n0 = blockIdx.x * BN;
+    // loads: 64 rows x 32 elements = 256 packets of 8; a thread two packets of A and two of W
+    const int g = lane >> 2, t = lane & 3;
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][e] = 0.0f;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int k0 = 0; k0 < K; k0 += MK) {
+        uint4 av[2], wv[2];
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+            const int packet = tid + p * 128;
+            const int r = packet >> 2, c = (packet & 3) * 8;
+            const int a = rows_of[r];
+            av[p] = a < 0 ? zero : *reinterpret_cast<const uint4*>(in + (int64_t)(a / top_div) * in_stride + k0 + c);
+            const int n = n0 + r;
+            wv[p] = n < N ? *reinterpret_cast<const uint4*>(We + (int64_t)n * K + k0 + c) : zero;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+            const int packet = tid + p * 128;
+            const int r = packet >> 2, c = (packet & 3) * 8;
+            *reinterpret_cast<uint4*>(&As[r][c]) = av[p];
+            *reinterpret_cast<uint4*>(&Ws[r][c]) = wv[p];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < MK; ks += 16) {
+            uint32_t a[4];
+            const int r = warp * 16 + g;
+            a[0] = *reinterpret_cast<const uint32_t*>(&As[r][ks + 2 * t]);
+            a[1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][ks + 2 * t]);
+            a[2] = *reinterpret_cast<const uint32_t*>(&As[r][ks + 2 * t + 8]);
+            a[3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][ks + 2 * t + 8]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint32_t b[2];
+                b[0] = *reinterpret_cast<const uint32_t*>(&Ws[j * 8 + g][ks + 2 * t]);
+                b[1] = *reinterpret_cast<const uint32_t*>(&Ws[j * 8 + g][ks + 2 * t + 8]);
+                mma_bf16_16816(acc[j], a, b);
+            }
+        }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int a = rows_of[warp * 16 + g + half * 8];
+        if (a < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int n = n0 + j * 8 + 2 * t + e;
+                if (n >= N) continue;
+                float v = acc[j][half * 2 + e];
+                if (EPI == EXP_SQUARED_RELU) {
+                    v = fmaxf(v, 0.0f);
+                    v *= v;
+                }
+                Elem<O>::store(out + (int64_t)a * out_stride + n, v);
+            }
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------- the weighted sum
+
+__global__ void expert_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
+                                      const float* __restrict__ base, float* __restrict__ out, int width, int top) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t row = blockIdx.x;
+    const float* w = weights + row * top;
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < width; j += gridDim.y * blockDim.x) {
+        float sum = 0.0f;
+        for (int s = 0; s < top; ++s) sum = fmaf(w[s], y[(row * top + s) * width + j], sum);
+        if (base != nullptr) sum += base[row * width + j];
+        out[row * width + j] = sum;
+    }
+}
+
+template <typename T, typename O>
+int launch_linear(const void* in, int64_t in_stride, const void* W, void* out, int64_t out_stride, const int* offsets,
+                  const int* order, int assignments, int experts, int top_div, int N, int K, int epilogue,
+                  cudaStream_t stream) {
+    const dim3 grid((N + BN - 1) / BN, (assignments + BM - 1) / BM + experts);
+    if (grid.y > 65535) return TB_ERR_BAD_SIZE;
+    cudaError_t launched;
+    if (epilogue == EXP_SQUARED_RELU)
+        launched = tb_launch_pdl(expert_linear_kernel<T, O, EXP_SQUARED_RELU>, grid, dim3(256), 0, stream, (const T*)in,
+                                 in_stride, (const T*)W, (O*)out, out_stride, offsets, order, experts, top_div, N, K);
+    else
+        launched = tb_launch_pdl(expert_linear_kernel<T, O, EXP_PLAIN>, grid, dim3(256), 0, stream, (const T*)in,
+                                 in_stride, (const T*)W, (O*)out, out_stride, offsets, order, experts, top_div, N, K);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
+template <typename O>
+int launch_linear_mma(const void* in, int64_t in_stride, const void* W, void* out, int64_t out_stride,
+                      const int* offsets, const int* order, int assignments, int experts, int top_div, int N, int K,
+                      int epilogue, cudaStream_t stream) {
+    const dim3 grid((N + BN - 1) / BN, (assignments + BM - 1) / BM + experts);
+    if (grid.y > 65535) return TB_ERR_BAD_SIZE;
+    cudaError_t launched;
+    if (epilogue == EXP_SQUARED_RELU)
+        launched = tb_launch_pdl(expert_linear_mma_kernel<O, EXP_SQUARED_RELU>, grid, dim3(128), 0, stream,
+                                 (const __nv_bfloat16*)in, in_stride, (const __nv_bfloat16*)W, (O*)out, out_stride,
+                                 offsets, order, experts, top_div, N, K);
+    else
+        launched = tb_launch_pdl(expert_linear_mma_kernel<O, EXP_PLAIN>, grid, dim3(128), 0, stream,
+                                 (const __nv_bfloat16*)in, in_stride, (const __nv_bfloat16*)W, (O*)out, out_stride,
+                                 offsets, order, experts, top_div, N, K);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
+}  // namespace
+
+// x: [rows, width] (row stride x_stride); router: 32-bit [experts, width]; ids: int32 [rows, top]; weights: 32-bit
+// [rows, top].
+TB_EXPORT int tb_route_topk(const void* x, int64_t x_stride, const float* router, int* ids, float* weights, int rows,
+                            int width, int experts, int top, int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (width < 1 || experts < 1 || top < 1 || top > experts) return TB_ERR_BAD_SIZE;
+    const int per_warp = rows >= 512 ? 4 : 1;
+    const size_t smem = (size_t)kRouteWarps * per_warp * (width + experts) * sizeof(float);
+    if (smem > 200 * 1024) return TB_ERR_BAD_SIZE;
+    const dim3 grid((rows + kRouteWarps * per_warp - 1) / (kRouteWarps * per_warp));
+    cudaError_t launched;
+#define TB_ROUTE(T, R)                                                                                              \
+    do {                                                                                                            \
+        auto kernel = route_topk_kernel<T, R>;                                                                      \
+        if (smem > 40 * 1024) {                                                                                     \
+            cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (err != cudaSuccess) return (int)err;                                                                \
+        }                                                                                                           \
+        launched = tb_launch_pdl(kernel, grid, dim3(kRouteWarps * 32), smem, stream, (const T*)x, x_stride, router, \
+                                 ids, weights, rows, width, experts, top);                                          \
+    } while (0)
+    if (dtype == TB_F32) {
+        if (per_warp == 4) TB_ROUTE(float, 4); else TB_ROUTE(float, 1);
+    } else if (dtype == TB_BF16) {
+        if (per_warp == 4) TB_ROUTE(__nv_bfloat16, 4); else TB_ROUTE(__nv_bfloat16, 1);
+    } else {
+        return TB_ERR_BAD_DTYPE;
+    }
+#undef TB_ROUTE
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
+// ids: int32 [assignments]; offsets: int32 [experts + 1]; order: int32 [assignments].
+TB_EXPORT int tb_expert_plan(const int* ids, int assignments, int experts, int* offsets, int* order,
+                             cudaStream_t stream) {
+    if (experts < 1 || experts > 8192 || assignments < 0) return TB_ERR_BAD_SIZE;
+    cudaError_t launched = tb_launch_pdl(expert_plan_kernel, dim3(1), dim3(1024), (size_t)2 * experts * sizeof(int),
+                                         stream, ids, assignments, experts, offsets, order);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
+// in: [*, K] of dtype (row stride in_stride); W: [experts, N, K] of dtype; out: [assignments, N] of out_dtype (row
+// stride out_stride); top_div: the source row of assignment a is a / top_div.  epilogue: 0 plain, 1 squared ReLU.
+// tensor_cores != 0 asks for the mma.sync kernel (bfloat16, K a multiple of 32, 16-byte aligned rows); the entry point
+// refuses it where it cannot run.
+TB_EXPORT int tb_expert_linear(const void* in, int64_t in_stride, const void* W, void* out, int64_t out_stride,
+                               const int* offsets, const int* order, int assignments, int experts, int top_div, int N,
+                               int K, int epilogue, int dtype, int out_dtype, int tensor_cores, cudaStream_t stream) {
+    if (assignments == 0 || N == 0) return 0;
+    if (K < 1 || top_div < 1 || experts < 1) return TB_ERR_BAD_SIZE;
+    if (epilogue != EXP_PLAIN && epilogue != EXP_SQUARED_RELU) return TB_ERR_BAD_SIZE;
+    if (tensor_cores) {
+        if (dtype != TB_BF16) return TB_ERR_BAD_DTYPE;
+        if (K % MK != 0 || in_stride % 8 != 0 || ((uintptr_t)in | (uintptr_t)W) % 16 != 0) return TB_ERR_BAD_ALIGN;
+        if (out_dtype == TB_F32)
+            return launch_linear_mma<float>(in, in_stride, W, out, out_stride, offsets, order, assignments, experts,
+                                            top_div, N, K, epilogue, stream);
+        if (out_dtype == TB_BF16)
+            return launch_linear_mma<__nv_bfloat16>(in, in_stride, W, out, out_stride, offsets, order, assignments,
+                                                    experts, top_div, N, K, epilogue, stream);
+        return TB_ERR_BAD_DTYPE;
+    }
+    if (dtype == TB_F32 && out_dtype == TB_F32)
+        return launch_linear<float, float>(in, in_stride, W, out, out_stride, offsets, order, assignments, experts,
+                                           top_div, N, K, epilogue, stream);
+    if (dtype == TB_BF16 && out_dtype == TB_F32)
+        return launch_linear<__nv_bfloat16, float>(in, in_stride, W, out, out_stride, offsets, order, assignments,
+                                                   experts, top_div, N, K, epilogue, stream);
+    if (dtype == TB_BF16 && out_dtype == TB_BF16)
+        return launch_linear<__nv_bfloat16, __nv_bfloat16>(in, in_stride, W, out, out_stride, offsets, order,
+                                                           assignments, experts, top_div, N, K, epilogue, stream);
+    return TB_ERR_BAD_DTYPE;
+}
+
+// y: 32-bit [rows * top, width]; weights: 32-bit [rows, top]; base: null or 32-bit [rows, width]; out: 32-bit
+// [rows, width] (may alias base).
+TB_EXPORT int tb_expert_combine(const float* y, const float* weights, const float* base, float* out, int rows,
+                                int width, int top, cudaStream_t stream) {
+    if (rows == 0 || width == 0) return 0;
+    if (top < 1) return TB_ERR_BAD_SIZE;
+    int by = (width + 255) / 256;
+    if (by > 32) by = 32;
+    cudaError_t launched = tb_launch_pdl(expert_combine_kernel, dim3(rows, by), dim3(256), 0, stream, y, weights, base,
+                                         out, width, top);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}

@@ -38,7 +38,7 @@ def graph_safe(model) -> bool:
     feed-forward, the embedding, the final norm and the head) declares ``graph_safe``, i.e. that everything which
     varies between two steps of the same shape reaches it through device tensors, never through a host-side field
     of the step context."""
-    parts = [model.embedding, model.final_norm, model.head]
+    parts = [model.embedding, model.final_norm, model.head] + list(getattr(model, "injections", ()))
     for block in model.layers:
         parts += [block.mixer, *block.norms.values()] + ([block.feed_forward] if block.feed_forward is not None else [])
     return all(getattr(part, "graph_safe", False) for part in parts)

@@ -852,3 +852,220 @@ def gated_recurrence(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Ten
                                    _ptr(state_slots), _i32(num_seqs), _i32(width), _i32(max_new), _stream()),
            "gated_recurrence")
     return out
+
+
+# ----------------------------------------------------------------------------- blocks whose two branches read one stream
+
+
+def _f32_rows(t: Optional[torch.Tensor], shape, what: str) -> None:
+    if t is not None:
+        _need(t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == tuple(shape), what)
+
+
+def sum_norms(residual: torch.Tensor, update_a: Optional[torch.Tensor], update_b: Optional[torch.Tensor],
+              weight1: torch.Tensor, out1: torch.Tensor, weight2: Optional[torch.Tensor], out2: Optional[torch.Tensor],
+              eps: float) -> None:
+    """``residual += update_a + update_b`` (32-bit, in place, each update optional; ``update_b`` needs ``update_a``), then
+    ``out1 = rms(residual) * weight1`` and, if given, ``out2 = rms(residual) * weight2`` from one read of the row:
+    two RMS norms of the same row share its statistic."""
+    _cuda(residual, update_a, update_b, weight1, out1, weight2, out2)
+    rows, width = residual.shape
+    _f32_rows(residual, (rows, width), "sum_norms: the stream is contiguous float32")
+    _f32_rows(update_a, (rows, width), "sum_norms update")
+    _f32_rows(update_b, (rows, width), "sum_norms update")
+    _need(update_b is None or update_a is not None, "sum_norms: a second update needs a first")
+    _need((weight2 is None) == (out2 is None), "sum_norms: the second norm needs its weight and its output")
+    for w in (weight1, weight2):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == width and w.is_contiguous()), "sum_norms weight")
+    for o in (out1, out2):
+        _need(o is None or (o.shape == residual.shape and o.is_contiguous() and o.dtype == out1.dtype), "sum_norms out")
+    lib = load_library("parallel_norm")
+    _check(lib.tb_sum_norms(_ptr(residual), _ptr(update_a), _ptr(update_b), _ptr(weight1), _ptr(out1), _ptr(weight2),
+                            _ptr(out2), _ptr(residual), _i32(rows), _i32(width), _f32(eps), _i32(_code(out1.dtype)),
+                            _stream()), "sum_norms")
+
+
+def sum_concat(residual: torch.Tensor, update_a: Optional[torch.Tensor], update_b: Optional[torch.Tensor],
+               origin: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[:, :W] = residual + (update_a + update_b)`` and ``out[:, W:] = origin`` (all inputs float32 ``[T, W]``; ``out``
+    ``[T, 2 W]`` float32 or bfloat16): a stream with its pending updates beside a second stream, ready for one product."""
+    _cuda(residual, update_a, update_b, origin, out)
+    rows, width = residual.shape
+    for t in (residual, update_a, update_b, origin):
+        _f32_rows(t, (rows, width), "sum_concat takes contiguous float32 [rows, width] tensors")
+    _need(update_b is None or update_a is not None, "sum_concat: a second update needs a first")
+    _need(tuple(out.shape) == (rows, 2 * width) and out.is_contiguous(), "sum_concat out")
+    lib = load_library("parallel_norm")
+    _check(lib.tb_sum_concat(_ptr(residual), _ptr(update_a), _ptr(update_b), _ptr(origin), _ptr(out), _i32(rows),
+                             _i32(width), _i32(_code(out.dtype)), _stream()), "sum_concat")
+    return out
+
+
+ACT_SILU, ACT_GELU_TANH = 0, 1
+
+
+def gated_activation(gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, activation: int) -> torch.Tensor:
+    """``out = act(gate + bias[:I]) * (up + bias[I:])``; gate and up are the two halves of ``gate_up``'s rows, ``bias``
+    (float32 ``[2 I]``) may be None; ``activation``: ``ACT_SILU`` or ``ACT_GELU_TANH``."""
+    _cuda(gate_up, bias, out)
+    rows, inter = out.shape
+    _need(gate_up.stride(1) == 1 and gate_up.shape == (rows, 2 * inter) and out.stride(1) == 1
+          and out.dtype == gate_up.dtype, "gated_activation gate_up/out")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * inter and bias.is_contiguous()),
+          "gated_activation bias")
+    lib = load_library("pointwise")
+    _check(lib.tb_gated_activation(_ptr(gate_up), _i64(gate_up.stride(0)), _ptr(bias), _ptr(out), _i64(out.stride(0)),
+                                   _i32(rows), _i32(inter), _i32(activation), _i32(_code(out.dtype)), _stream()),
+           "gated_activation")
+    return out
+
+
+def squared_relu(z: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = max(z, 0)^2`` (``out`` may be ``z``)."""
+    _cuda(z, out)
+    _need(z.stride(1) == 1 and out.stride(1) == 1 and out.shape == z.shape and out.dtype == z.dtype, "squared_relu z/out")
+    lib = load_library("pointwise")
+    _check(lib.tb_squared_relu(_ptr(z), _i64(z.stride(0)), _ptr(out), _i64(out.stride(0)), _i32(z.shape[0]),
+                               _i32(z.shape[1]), _i32(_code(z.dtype)), _stream()), "squared_relu")
+    return out
+
+
+def add_bias(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """``y += bias`` row by row, in place (``bias`` float32 ``[width]``)."""
+    _cuda(y, bias)
+    _need(y.stride(1) == 1 and bias.dtype == torch.float32 and bias.numel() == y.shape[1] and bias.is_contiguous(),
+          "add_bias y/bias")
+    lib = load_library("pointwise")
+    _check(lib.tb_add_bias(_ptr(y), _i64(y.stride(0)), _ptr(bias), _i32(y.shape[0]), _i32(y.shape[1]),
+                           _i32(_code(y.dtype)), _stream()), "add_bias")
+    return y
+
+
+def scale_rows(y: torch.Tensor, factor: float) -> torch.Tensor:
+    """``y *= factor`` in place (contiguous float32)."""
+    _cuda(y)
+    _need(y.dtype == torch.float32 and y.is_contiguous(), "scale_rows takes a contiguous float32 tensor")
+    lib = load_library("pointwise")
+    _check(lib.tb_scale_rows(_ptr(y), _i64(y.numel()), _f32(factor), _stream()), "scale_rows")
+    return y
+
+
+def add_rows(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a += b`` in place (contiguous float32 tensors of one shape)."""
+    _cuda(a, b)
+    _need(a.dtype == torch.float32 and b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous()
+          and a.shape == b.shape, "add_rows takes two contiguous float32 tensors of one shape")
+    lib = load_library("pointwise")
+    _check(lib.tb_add_rows(_ptr(a), _ptr(b), _i64(a.numel()), _stream()), "add_rows")
+    return a
+
+
+def embedding_scaled(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, factor: float) -> torch.Tensor:
+    """``out[t] = float32(table[tokens[t]]) * factor`` for a float32 ``out``."""
+    _cuda(tokens, table, out)
+    _need(tokens.dtype == torch.int32 and tokens.is_contiguous(), "tokens must be contiguous int32")
+    _need(out.dtype == torch.float32 and table.is_contiguous() and out.is_contiguous(), "embedding_scaled table/out")
+    rows, hidden = out.shape
+    _need(tokens.numel() == rows and table.shape[1] == hidden, "embedding shapes disagree")
+    lib = load_library("pointwise")
+    _check(lib.tb_embedding_scaled(_ptr(tokens), _ptr(table), _i32(_code(table.dtype)), _ptr(out), _i32(rows),
+                                   _i32(hidden), _i32(table.shape[0]), _f32(factor), _stream()), "embedding_scaled")
+    return out
+
+
+def rope_norm_cache(proj: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
+                    seq_of_row: torch.Tensor, block_table: torch.Tensor, inv_freq: Optional[torch.Tensor], *,
+                    amplitude: float, heads: int, kv_heads: int, dim: int, vdim: int, rot_dims: int,
+                    unit_norm: bool, eps: float, page_size: int, write_kv: bool = True) -> None:
+    """Rotate-half rotation of the first ``rot_dims`` numbers of every query and key head of ``proj`` (cosine and sine
+    times ``amplitude``), then, with ``unit_norm``, every head over ``sqrt(mean(head^2) + eps)``; queries into ``q_out``,
+    keys and values into the pages of ``cache`` (``[kv_heads, page, dim]`` keys then ``[kv_heads, page, vdim]`` values)."""
+    _cuda(proj, q_out, cache, positions, seq_of_row, block_table, inv_freq)
+    rows = q_out.shape[0]
+    channels = heads * dim + kv_heads * (dim + vdim)
+    _need(proj.stride(1) == 1 and proj.shape[1] >= channels and proj.shape[0] == rows, "rope_norm_cache proj")
+    _need(q_out.stride(1) == 1 and q_out.shape[1] == heads * dim and q_out.dtype == proj.dtype, "rope_norm_cache q_out")
+    _need(cache.dtype == proj.dtype and cache.is_contiguous(), "rope_norm_cache cache dtype")
+    if rot_dims:
+        _need(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2
+              and inv_freq.is_contiguous(), "rope_norm_cache inv_freq")
+    for t in (positions, seq_of_row, block_table):
+        _need(t.dtype == torch.int32, "rope_norm_cache metadata must be int32")
+    lib = load_library("rope_norm_cache")
+    _check(lib.tb_rope_norm_cache(_ptr(proj), _i64(proj.stride(0)), _ptr(q_out), _i64(q_out.stride(0)), _ptr(cache),
+                                  _ptr(positions), _ptr(seq_of_row), _ptr(block_table), _i32(block_table.stride(0)),
+                                  _ptr(inv_freq), _f32(amplitude), _i32(rows), _i32(heads), _i32(kv_heads), _i32(dim),
+                                  _i32(vdim), _i32(rot_dims), _i32(1 if unit_norm else 0), _f32(eps), _i32(page_size),
+                                  _i32(1 if write_kv else 0), _i32(_code(proj.dtype)), _stream()), "rope_norm_cache")
+
+
+# ----------------------------------------------------------------------------- routed experts
+
+EXPERT_PLAIN, EXPERT_SQUARED_RELU = 0, 1
+
+
+def route_topk(x: torch.Tensor, router: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """Router logits ``x @ router^T`` in 32-bit (``router`` float32 ``[E, W]``), the ``top`` largest per row (largest
+    first) into ``ids`` (int32 ``[T, top]``) and the softmax over those into ``weights`` (float32 ``[T, top]``)."""
+    _cuda(x, router, ids, weights)
+    rows, width = x.shape
+    top = ids.shape[1]
+    _need(x.stride(1) == 1, "route_topk x")
+    _need(router.dtype == torch.float32 and router.is_contiguous() and router.shape[1] == width, "route_topk router")
+    _need(ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (rows, top), "route_topk ids")
+    _need(weights.dtype == torch.float32 and weights.is_contiguous() and weights.shape == (rows, top), "route_topk weights")
+    lib = load_library("experts")
+    _check(lib.tb_route_topk(_ptr(x), _i64(x.stride(0)), _ptr(router), _ptr(ids), _ptr(weights), _i32(rows), _i32(width),
+                             _i32(router.shape[0]), _i32(top), _i32(_code(x.dtype)), _stream()), "route_topk")
+
+
+def expert_plan(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: torch.Tensor) -> None:
+    """Group the assignments ``ids.flatten()`` by expert: ``order[offsets[e] : offsets[e + 1]]`` are expert ``e``'s."""
+    _cuda(ids, offsets, order)
+    count = ids.numel()
+    _need(ids.dtype == torch.int32 and ids.is_contiguous(), "expert_plan ids")
+    _need(offsets.dtype == torch.int32 and offsets.numel() == experts + 1 and offsets.is_contiguous(), "expert_plan offsets")
+    _need(order.dtype == torch.int32 and order.numel() == count and order.is_contiguous(), "expert_plan order")
+    lib = load_library("experts")
+    _check(lib.tb_expert_plan(_ptr(ids), _i32(count), _i32(experts), _ptr(offsets), _ptr(order), _stream()), "expert_plan")
+
+
+def expert_linear_tensor_cores(dtype: torch.dtype, in_features: int) -> bool:
+    """Whether the experts' product of these sizes runs on the tensor cores (bfloat16, K a multiple of 32)."""
+    return dtype == torch.bfloat16 and in_features % 32 == 0
+
+
+def expert_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor,
+                  *, source_div: int, epilogue: int = EXPERT_PLAIN) -> torch.Tensor:
+    """``out[a] = act(weight[expert(a)] @ x[a // source_div])`` for every assignment ``a`` (``weight`` ``[E, N, K]``,
+    ``out`` ``[assignments, N]`` in ``x``'s dtype or float32), grouped as ``expert_plan`` left them."""
+    _cuda(x, weight, out, offsets, order)
+    experts, n, k = weight.shape
+    count = out.shape[0]
+    _need(x.stride(1) == 1 and x.shape[1] == k and weight.is_contiguous() and weight.dtype == x.dtype, "expert_linear x/weight")
+    _need(out.stride(1) == 1 and out.shape[1] == n and out.dtype in (x.dtype, torch.float32), "expert_linear out")
+    _need(order.numel() == count and offsets.numel() == experts + 1, "expert_linear plan")
+    _need(x.shape[0] * source_div >= count, "expert_linear: sources do not cover the assignments")
+    tensor_cores = (expert_linear_tensor_cores(x.dtype, k) and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+                    and weight.data_ptr() % 16 == 0)
+    lib = load_library("experts")
+    _check(lib.tb_expert_linear(_ptr(x), _i64(x.stride(0)), _ptr(weight), _ptr(out), _i64(out.stride(0)), _ptr(offsets),
+                                _ptr(order), _i32(count), _i32(experts), _i32(source_div), _i32(n), _i32(k),
+                                _i32(epilogue), _i32(_code(x.dtype)), _i32(_code(out.dtype)),
+                                _i32(1 if tensor_cores else 0), _stream()), "expert_linear")
+    return out
+
+
+def expert_combine(y: torch.Tensor, weights: torch.Tensor, base: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+    """``out[t] = (base[t] if base is given else 0) + sum_s weights[t, s] * y[t * top + s]``, all float32."""
+    _cuda(y, weights, base, out)
+    rows, width = out.shape
+    top = weights.shape[1]
+    _f32_rows(y, (rows * top, width), "expert_combine y")
+    _f32_rows(weights, (rows, top), "expert_combine weights")
+    _f32_rows(base, (rows, width), "expert_combine base")
+    _f32_rows(out, (rows, width), "expert_combine out")
+    lib = load_library("experts")
+    _check(lib.tb_expert_combine(_ptr(y), _ptr(weights), _ptr(base), _ptr(out), _i32(rows), _i32(width), _i32(top),
+                                 _stream()), "expert_combine")
+    return out

@@ -16,7 +16,7 @@ import torch
 
 from .. import kernels
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
-from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, Block, CacheBinding, DeferredNorm,
+from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, INJECTIONS, MIXERS, NORMS, Block, CacheBinding, DeferredNorm,
                      ResidualStream, Runtime, StepContext)
 from ..weights.loader import ExpectedTensor
 
@@ -35,6 +35,8 @@ def _part_specs(spec: ModelSpec):
         yield MIXERS, layer.mixer
         if layer.feed_forward is not None:
             yield FEED_FORWARDS, layer.feed_forward
+    for injection in spec.injections:
+        yield INJECTIONS, injection
     yield NORMS, spec.final_norm
     yield HEADS, spec.head
 
@@ -82,6 +84,7 @@ class DecoderModel:
             mixer = build(MIXERS, layer.mixer)
             feed_forward = build(FEED_FORWARDS, layer.feed_forward) if layer.feed_forward is not None else None
             self.layers.append(block_cls(norms, mixer, feed_forward))
+        self.injections = [build(INJECTIONS, part) for part in spec.injections]
         self.final_norm = build(NORMS, spec.final_norm)
         # A head that names the embedding's checkpoint tensor (tied embeddings) gets the same host tensor, and the
         # runtime hands it the device copy that the embedding made: tying is a matter of tensor names alone.
@@ -113,10 +116,14 @@ class DecoderModel:
         hidden = self.embedding.forward(ctx.token_ids[:ctx.num_rows])
         stream = ResidualStream(hidden, None)
         order = self.spec.run_order
+        # the embedding output that injections read: rows of their own, since blocks add into the stream in place
+        origin = self.embedding.forward(ctx.token_ids[:ctx.num_rows]) if self.injections else None
         wants_logits = want_rows is not None and want_rows.numel() > 0
         every_row = wants_logits and want_every_row and want_rows.numel() == ctx.num_rows
         for index, entry in enumerate(order):
             block = self.layers[entry.layer]
+            if entry.inject is not None:
+                stream = self.injections[entry.inject].forward(stream, origin, ctx)
             if not block.accepts_next_norm:
                 stream = block.forward(stream, ctx, bindings[index])
                 continue
@@ -136,14 +143,16 @@ class DecoderModel:
         width = stream.residual.shape[1]
         if every_row and stream.prepared is not None and stream.prepared.norm is self.final_norm:
             return self.head.forward(stream.prepared if self.head.accepts_deferred_norm else stream.prepared.materialize())
+        pending = [stream.update, stream.update_b]
         if every_row:
-            residual, update = stream.residual[:count], None if stream.update is None else stream.update[:count]
+            residual = stream.residual[:count]
+            pending = [None if u is None else u[:count] for u in pending]
         else:
             residual = torch.empty((count, width), dtype=stream.residual.dtype, device=stream.residual.device)
             kernels.gather_rows(want_rows, stream.residual, residual)
-            update = None
-            if stream.update is not None:
-                update = torch.empty_like(residual)
-                kernels.gather_rows(want_rows, stream.update, update)
-        final = DeferredNorm(self.final_norm, residual, update)
+            for index, update in enumerate(pending):
+                if update is not None:
+                    pending[index] = kernels.gather_rows(want_rows, update, torch.empty((count, update.shape[1]), dtype=update.dtype,
+                                                                                 device=update.device))
+        final = DeferredNorm(self.final_norm, residual, pending[0], pending[1])
         return self.head.forward(final if self.head.accepts_deferred_norm else final.materialize())

@@ -25,6 +25,9 @@ Kinds and what each must provide:
     :class:`ResidualStream`.
 ``Embedding`` / ``Head``
     ``forward(token_ids)`` -> ``[T, hidden]`` / ``forward(x)`` -> float32 ``[S, vocab]``.
+``Injection``
+    ``forward(stream, origin, ctx)`` -> the new :class:`ResidualStream`: a step between two blocks that mixes the
+    stream with the embedding output.
 
 Every class also has ``expected_tensors(spec)`` -> ``{checkpoint name: ExpectedTensor}``
 so that the loader can check a checkpoint, and the random-weights writer can make one,
@@ -257,6 +260,9 @@ class ResidualStream:
     residual: torch.Tensor
     update: Optional[torch.Tensor] = None
     prepared: Optional["PreparedNorm"] = None
+    # a second pending update (a block whose mixer and feed-forward both read the same stream leaves two): the
+    # stream is ``residual + (update + update_b)``
+    update_b: Optional[torch.Tensor] = None
 
 
 class DeferredNorm:
@@ -268,10 +274,12 @@ class DeferredNorm:
     Either way ``residual`` afterwards is the updated residual stream.
     """
 
-    def __init__(self, norm: "Norm", residual: torch.Tensor, update: Optional[torch.Tensor]):
+    def __init__(self, norm: "Norm", residual: torch.Tensor, update: Optional[torch.Tensor],
+                 update_b: Optional[torch.Tensor] = None):
         self.norm = norm
         self.residual = residual
         self.update = update
+        self.update_b = update_b
         self._value: Optional[torch.Tensor] = None
         self.done = False
 
@@ -281,7 +289,9 @@ class DeferredNorm:
 
     def materialize(self) -> torch.Tensor:
         if self._value is None:
-            if self.update is None:
+            if self.update_b is not None:
+                self._value = self.norm.forward_sum(self.residual, self.update, self.update_b)
+            elif self.update is None:
                 self._value = self.norm.forward(self.residual)
             else:
                 self._value = self.norm.forward_add(self.residual, self.update)   # residual += update, in place
@@ -353,6 +363,20 @@ class Norm(Part):
                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
+    def forward_sum(self, residual: torch.Tensor, update_a: Optional[torch.Tensor], update_b: Optional[torch.Tensor],
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The norm of ``residual + (update_a + update_b)`` (either update may be None; the sum is stored back into
+        ``residual``): what follows a block whose mixer and feed-forward ran side by side.  A norm with a kernel
+        for it overrides this; here the two updates are added first (32-bit, into ``update_a``)."""
+        from .. import kernels
+
+        if update_a is None or update_b is None:
+            update = update_a if update_a is not None else update_b
+            return self.forward(residual, out) if update is None else self.forward_add(residual, update, out)
+        if update_a.dtype != torch.float32 or update_b.dtype != torch.float32:
+            raise NotImplementedError(f"norm '{self.kind}' cannot add two updates that are not 32-bit")
+        return self.forward_add(residual, kernels.add_rows(update_a, update_b), out)
+
 
 class PositionEncoding(Part):
     rotary_inv_freq: Optional[torch.Tensor] = None
@@ -384,6 +408,15 @@ class FeedForward(Part):
 
 class Embedding(Part):
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Injection(Part):
+    """A transformation of the whole stream between two blocks that also reads the embedding output (``origin``,
+    the rows as the embedding left them, never written afterwards): ``forward(stream, origin, ctx)`` returns the new
+    stream.  The model description says in front of which run entries one stands."""
+
+    def forward(self, stream: "ResidualStream", origin: torch.Tensor, ctx: StepContext) -> "ResidualStream":
         raise NotImplementedError
 
 
@@ -425,3 +458,4 @@ FEED_FORWARDS: Registry[FeedForward] = Registry("feed-forward")
 BLOCKS: Registry[Block] = Registry("block")
 EMBEDDINGS: Registry[Embedding] = Registry("embedding")
 HEADS: Registry[Head] = Registry("head")
+INJECTIONS: Registry[Injection] = Registry("injection")

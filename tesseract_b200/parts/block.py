@@ -12,6 +12,16 @@ block's norm, and the role ``post_mixer`` needs no norm.
 
 Each addition is fused into the norm that follows it; where the part in front can, its last product does that
 norm's work on the way out (``FollowNorm`` -> ``PreparedNorm``), and the product behind only applies the scale.
+
+``parallel`` lets the mixer and the feed-forward read the same stream, each through a norm of its own, and adds
+both results:
+
+    x  = residual [+ pending updates]
+    a  = mixer(mixer_norm(x))
+    f  = feed_forward(feed_forward_norm(x))     -> leaves (x, a, f): the stream is x + (a + f)
+
+Two RMS norms of one row share the row's statistic, so where both norms say so (``shared_statistic``) the pending
+sum and both norms are one kernel.  A layer without a feed-forward leaves (x, a).
 """
 
 from __future__ import annotations
@@ -39,7 +49,7 @@ class PreNormBlock(Block):
         if stream.prepared is not None and stream.prepared.norm is self.norms["input"]:
             first = stream.prepared                       # the block in front already did this norm's work
         else:
-            first = DeferredNorm(self.norms["input"], stream.residual, stream.update)
+            first = DeferredNorm(self.norms["input"], stream.residual, stream.update, stream.update_b)
         x = first if self.mixer.accepts_deferred_norm else first.materialize()
         if self.feed_forward is None:
             return ResidualStream(first.residual, self.mixer.forward(x, ctx, cache))
@@ -56,3 +66,45 @@ class PreNormBlock(Block):
         if isinstance(update, PreparedNorm):
             return ResidualStream(update.residual, None, prepared=update)
         return ResidualStream(second.residual, update)
+
+
+@BLOCKS.register("parallel")
+class ParallelBlock(Block):
+    @classmethod
+    def norm_roles(cls, with_feed_forward: bool = True) -> Tuple[str, ...]:
+        return ("mixer", "feed_forward") if with_feed_forward else ("mixer",)
+
+    def entry_norm(self) -> Optional[Norm]:
+        return self.norms["mixer"]
+
+    def _norms_of_sum(self, stream: ResidualStream):
+        """``(x for the mixer, x for the feed-forward or None)``; afterwards ``stream.residual`` holds the sum."""
+        import torch
+
+        from .. import kernels
+
+        first, second = self.norms["mixer"], self.norms.get("feed_forward") if self.feed_forward is not None else None
+        residual = stream.residual
+        one = getattr(first, "shared_statistic", lambda: None)()
+        two = getattr(second, "shared_statistic", lambda: None)() if second is not None else None
+        updates = [u for u in (stream.update, stream.update_b) if u is not None]
+        shared = (one is not None and two is not None and one[1] == two[1] and residual.dtype == torch.float32
+                  and residual.is_contiguous() and all(u.dtype == torch.float32 and u.is_contiguous() for u in updates))
+        if shared:
+            dtype = first.runtime.dtype
+            x_mixer = torch.empty(residual.shape, dtype=dtype, device=residual.device)
+            x_feed = torch.empty_like(x_mixer)
+            kernels.sum_norms(residual, updates[0] if updates else None, updates[1] if len(updates) > 1 else None,
+                              one[0], x_mixer, two[0], x_feed, one[1])
+            return x_mixer, x_feed
+        x_mixer = DeferredNorm(first, residual, stream.update, stream.update_b).materialize()
+        return x_mixer, (second.forward(residual) if second is not None else None)
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: Optional[CacheBinding]) -> ResidualStream:
+        if stream.prepared is not None:
+            raise NotImplementedError("a parallel block takes the stream as a residual and its pending updates")
+        x_mixer, x_feed = self._norms_of_sum(stream)
+        mixed = self.mixer.forward(x_mixer, ctx, cache)
+        if self.feed_forward is None:
+            return ResidualStream(stream.residual, mixed)
+        return ResidualStream(stream.residual, mixed, update_b=self.feed_forward.forward(x_feed, ctx))

@@ -21,7 +21,8 @@ from .linear import BestOfRows, Linear
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
     """params: ``vocab_size, hidden_size``, optional ``stream`` (``"float32"``: the rows come out in 32-bit whatever
-    the run dtype, for a model whose residual stream is kept in 32-bit); weights: ``table``."""
+    the run dtype, for a model whose residual stream is kept in 32-bit), optional ``scale`` (the rows are multiplied
+    by it, in 32-bit: needs the 32-bit stream); weights: ``table``."""
 
     graph_safe = True
 
@@ -34,6 +35,9 @@ class TokenEmbedding(Embedding):
         if stream not in (None, "float32"):
             raise ValueError(f"an embedding's stream is the run dtype or 'float32', got '{stream}'")
         self.widen = stream == "float32" and self.table.dtype != torch.float32
+        self.scale = float(spec.params.get("scale") or 1.0)
+        if self.scale != 1.0 and stream != "float32":
+            raise ValueError("a scaled embedding feeds a residual stream kept in 32-bit (stream='float32')")
 
     @classmethod
     def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
@@ -41,6 +45,10 @@ class TokenEmbedding(Embedding):
         return {spec.weights["table"]: ExpectedTensor((int(p["vocab_size"]), int(p["hidden_size"])))}
 
     def forward(self, token_ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.scale != 1.0:
+            if out is None:
+                out = torch.empty((token_ids.numel(), self.hidden_size), dtype=torch.float32, device=self.table.device)
+            return kernels.embedding_scaled(token_ids, self.table, out, self.scale)
         if self.widen:
             if out is None:
                 out = torch.empty((token_ids.numel(), self.hidden_size), dtype=torch.float32, device=self.table.device)
@@ -52,7 +60,8 @@ class TokenEmbedding(Embedding):
 
 @HEADS.register("lm_head")
 class LMHead(Head):
-    """params: ``vocab_size, hidden_size``; weights: ``weight``.  Returns float32 logits."""
+    """params: ``vocab_size, hidden_size``, optional ``scale`` (the logits are multiplied by it); weights: ``weight``.
+    Returns float32 logits."""
 
     graph_safe = True
 
@@ -63,7 +72,9 @@ class LMHead(Head):
         self.proj = Linear(tensors["weight"], runtime)     # the embedding's device copy if both name one tensor
         # per-CTA best logit of each row, left by the product when it is the weight-streaming kernel (at most 16
         # rows): the sampler then need not read the logits again to find a row's best token
-        self.best = BestOfRows(runtime.device) if not runtime.is_float32 else None
+        self.scale = float(spec.params.get("scale") or 1.0)
+        # (scaled logits are scaled behind the product, so the product's own best-of-row values would not be theirs)
+        self.best = BestOfRows(runtime.device) if not runtime.is_float32 and self.scale == 1.0 else None
 
     @classmethod
     def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
@@ -80,9 +91,10 @@ class LMHead(Head):
         if isinstance(x, DeferredNorm):
             logits = self.proj.forward_normed(x, float32_out=True, best=self.best)
             if logits is not None:
-                return logits
+                return logits if self.scale == 1.0 else kernels.scale_rows(logits, self.scale)
             x = x.materialize()
-        return self.proj.forward(x, out=out, float32_out=True, best=self.best)
+        logits = self.proj.forward(x, out=out, float32_out=True, best=self.best)
+        return logits if self.scale == 1.0 else kernels.scale_rows(logits, self.scale)
 
     def argmax_partials(self):
         """``(values, indices)`` that the last ``forward`` left for the sampler, or None if it left none."""

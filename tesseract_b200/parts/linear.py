@@ -44,10 +44,15 @@ def _tma_rows(x: torch.Tensor) -> torch.Tensor:
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, runtime: Runtime):
+    def __init__(self, weight: torch.Tensor, runtime: Runtime, bias: Optional[torch.Tensor] = None):
+        """``bias`` (``[out]``, kept in 32-bit) is added to the stored product by a kernel of its own behind the
+        product's; the folded forms (a norm in front, a following norm's work behind, an activation) take no bias."""
         self.runtime = runtime
         self.weight = runtime.matrix(weight)
         self.out_features, self.in_features = self.weight.shape
+        self.bias = None if bias is None else runtime.vector_f32(bias)
+        if self.bias is not None and self.bias.numel() != self.out_features:
+            raise ValueError(f"a bias of {self.bias.numel()} numbers on a product of {self.out_features} features")
 
     def plan(self, rows: int, epilogue: str = plan.BF16, norm: Optional[str] = None,
              contiguous_rows: bool = True, follow: bool = False) -> plan.ProductPlan:
@@ -60,6 +65,15 @@ class Linear:
         return torch.empty((rows, width), dtype=dtype, device=device)
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, float32_out: bool = False,
+                epilogue: Optional[str] = None, follow=None, best=None):
+        """:meth:`product`, and the bias, if the product has one, added to the stored rows."""
+        if self.bias is None:
+            return self.product(x, out, float32_out, epilogue, follow, best)
+        if epilogue is not None or follow is not None or best is not None:
+            raise NotImplementedError("a product with a bias stores plain rows")
+        return kernels.add_bias(self.product(x, out, float32_out), self.bias)
+
+    def product(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, float32_out: bool = False,
                 epilogue: Optional[str] = None, follow=None, best=None):
         """``x @ W^T``; with ``epilogue="swiglu"`` the activated product ``[rows, out / 2]`` if the plan has a kernel
         that folds the activation in, else ``None`` (the caller then activates the plain product itself).  With
@@ -133,7 +147,8 @@ class Linear:
         from .base import PreparedNorm
 
         parameters = getattr(deferred.norm, "rms_parameters", None)
-        if parameters is None or deferred.done or not deferred.residual.is_contiguous():
+        if (parameters is None or deferred.done or not deferred.residual.is_contiguous()
+                or getattr(deferred, "update_b", None) is not None):
             return None
         wanted = epilogue or (plan.F32 if float32_out else plan.BF16)
         if isinstance(deferred, PreparedNorm):

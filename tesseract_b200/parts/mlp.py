@@ -119,3 +119,65 @@ class PolyNormMLP(FeedForward):
         z = self.up_proj.forward(x)
         kernels.polynorm(z, self.coefficients, self.eps, z)        # in place: a row is read whole before it is written
         return self.down_proj.forward(z, float32_out=self.stream_f32)
+
+
+_ACTIVATIONS = {"silu": kernels.ACT_SILU, "gelu_tanh": kernels.ACT_GELU_TANH}
+
+
+@FEED_FORWARDS.register("gated_mlp")
+class GatedMLP(FeedForward):
+    """A gated feed-forward ``down(act(gate h + bg) * (up h + bu)) + bd`` with a choice of activation and optional biases.
+
+    params: ``hidden_size, intermediate_size``, ``activation`` (``"silu"`` or ``"gelu_tanh"``: ``0.5 z (1 + tanh(sqrt(2/pi)
+    (z + 0.044715 z^3)))``), ``bias`` (bool), optional ``stream``; weights: ``gate, up, down`` and, with ``bias``,
+    ``gate_bias, up_bias, down_bias``.  Gate and up are one product; biases, activation and the gating are one kernel
+    in 32-bit behind it; the down product comes out in 32-bit for a residual stream kept in 32-bit."""
+
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        super().__init__(spec, tensors, runtime)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.intermediate_size = int(p["intermediate_size"])
+        if p.get("activation") not in _ACTIVATIONS:
+            raise ValueError(f"activation must be one of {sorted(_ACTIVATIONS)}, got {p.get('activation')!r}")
+        self.activation = _ACTIVATIONS[p["activation"]]
+        self.biased = bool(p.get("bias"))
+        self.stream_f32 = p.get("stream") == "float32"
+        self.gate_up_proj = Linear(torch.cat([tensors["gate"], tensors["up"]], dim=0), runtime)
+        self.gate_up_bias = None
+        if self.biased:
+            self.gate_up_bias = torch.cat([tensors["gate_bias"], tensors["up_bias"]]).to(
+                device=runtime.device, dtype=torch.float32).contiguous()
+        self.down_proj = Linear(tensors["down"], runtime, bias=tensors["down_bias"] if self.biased else None)
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
+        p, w = spec.params, spec.weights
+        hidden, inter = int(p["hidden_size"]), int(p["intermediate_size"])
+        out = {w["gate"]: ExpectedTensor((inter, hidden)), w["up"]: ExpectedTensor((inter, hidden)),
+               w["down"]: ExpectedTensor((hidden, inter))}
+        if p.get("bias"):
+            out.update({w["gate_bias"]: ExpectedTensor((inter,)), w["up_bias"]: ExpectedTensor((inter,)),
+                        w["down_bias"]: ExpectedTensor((hidden,))})
+        return out
+
+    @classmethod
+    def random_tensor(cls, spec, role, shape, generator) -> torch.Tensor:
+        if role.endswith("_bias"):
+            return torch.randn(shape, generator=generator, dtype=torch.float32) * 0.3
+        return torch.randn(shape, generator=generator, dtype=torch.float32) * (shape[-1] ** -0.5)
+
+    def products(self):
+        """``(name, Linear, epilogue)`` of the feed-forward's matrix products, for the printed kernel plan."""
+        return [("gate/up", self.gate_up_proj, plan.BF16),
+                ("down", self.down_proj, plan.F32 if self.stream_f32 else plan.BF16)]
+
+    def forward(self, x, ctx: StepContext, follow=None):
+        if isinstance(x, DeferredNorm):
+            x = x.materialize()
+        gate_up = self.gate_up_proj.forward(x)
+        activated = torch.empty((x.shape[0], self.intermediate_size), dtype=gate_up.dtype, device=gate_up.device)
+        kernels.gated_activation(gate_up, self.gate_up_bias, activated, self.activation)
+        return self.down_proj.forward(activated, float32_out=self.stream_f32)

@@ -60,9 +60,10 @@ class RMSNorm(Norm):
 class GroupedRMSNorm(Norm):
     """RMS norm over equal consecutive parts of the vector, for a residual stream kept in 32-bit.
 
-    params: ``size``, ``groups``, ``eps``; weights: ``weight`` ``[size]``.  The row is cut into ``groups`` parts, each
-    is divided by its own ``sqrt(mean(part^2) + eps)``, and the whole is multiplied by ``weight``; ``groups = 1`` is
-    the plain norm.  The stream (``x`` / ``residual``) is float32 whatever the run dtype, an update may be float32
+    params: ``size``, ``groups``, ``eps``, optional ``offset``; weights: ``weight`` ``[size]``.  The row is cut into
+    ``groups`` parts, each is divided by its own ``sqrt(mean(part^2) + eps)``, and the whole is multiplied by
+    ``offset + weight`` (``offset`` 0 unless given: a checkpoint that stores its norm weights around zero has
+    ``offset`` 1; the sum is taken once, in 32-bit, when the model is built); ``groups = 1`` is the plain norm.  The stream (``x`` / ``residual``) is float32 whatever the run dtype, an update may be float32
     or bfloat16, and the normalised rows come out in the run dtype, rounded once."""
 
     graph_safe = True
@@ -75,7 +76,10 @@ class GroupedRMSNorm(Norm):
         self.eps = float(params["eps"])
         if self.groups < 1 or self.size % self.groups:
             raise ValueError(f"a norm over {self.groups} groups needs a size that they divide, got {self.size}")
+        self.offset = float(params.get("offset") or 0.0)
         self.weight = runtime.vector_f32(tensors["weight"])
+        if self.offset:
+            self.weight = self.weight + self.offset
 
     @classmethod
     def expected_tensors(cls, spec: PartSpec) -> Dict[str, ExpectedTensor]:
@@ -83,7 +87,23 @@ class GroupedRMSNorm(Norm):
 
     @classmethod
     def random_tensor(cls, spec, role, shape: Tuple[int, ...], generator) -> torch.Tensor:
-        return 1.0 + torch.randn(shape, generator=generator, dtype=torch.float32) * 0.1
+        centre = 1.0 - float(spec.params.get("offset") or 0.0)
+        return centre + torch.randn(shape, generator=generator, dtype=torch.float32) * 0.1
+
+    def shared_statistic(self) -> Optional[Tuple[torch.Tensor, float]]:
+        """``(weight, eps)`` if this is a plain RMS norm over the whole row of a 32-bit stream (one group): two such
+        norms of the same row with the same ``eps`` differ in their weights only and may leave one kernel together."""
+        return (self.weight, self.eps) if self.groups == 1 else None
+
+    def forward_sum(self, residual: torch.Tensor, update_a: Optional[torch.Tensor], update_b: Optional[torch.Tensor],
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``residual += update_a + update_b`` (either may be None; 32-bit, in place), then the norm of the sum."""
+        if self.groups == 1 and all(u is None or u.dtype == torch.float32 for u in (update_a, update_b)):
+            first, second = (update_a, update_b) if update_a is not None else (update_b, None)
+            out = self._out(residual, out)
+            kernels.sum_norms(residual, first, second, self.weight, out, None, None, self.eps)
+            return out
+        return super().forward_sum(residual, update_a, update_b, out)
 
     def _out(self, x: torch.Tensor, out: Optional[torch.Tensor]) -> torch.Tensor:
         return out if out is not None else torch.empty(x.shape, dtype=self.runtime.dtype, device=x.device)

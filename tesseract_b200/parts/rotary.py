@@ -94,6 +94,59 @@ class RotaryPairs(PositionEncoding):
         raise NotImplementedError("the pair rotation is applied by the mixer's convolve-rotate-and-store kernel")
 
 
+def blended_inverse_frequencies(dims: int, base: float, scaling: Optional[Mapping[str, float]]):
+    """``(float64 [dims / 2] frequencies, amplitude)`` of a rotation whose context was stretched by ``factor``.
+
+    Plain frequencies are ``f_i = base^(-2i / dims)``.  With ``scaling`` (``factor``, ``original``, ``fast``, ``slow``)
+    every frequency becomes ``f_i / factor * r_i + f_i * (1 - r_i)``: the index at which ``original`` positions make
+    ``t`` full turns is ``n(t) = dims * ln(original / (2 pi t)) / (2 ln base)``; ``r`` rises linearly over the index
+    from 0 at ``max(floor(n(fast)), 0)`` to 1 at ``min(ceil(n(slow)), dims - 1)`` (a span of at least 0.001) and is
+    clamped outside.  Cosine and sine are both multiplied by the amplitude ``0.1 ln(factor) + 1``."""
+    half = dims // 2
+    plain = np.asarray([base ** (-2.0 * i / dims) for i in range(half)], dtype=np.float64)
+    if not scaling:
+        return plain, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def turns_index(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    low = max(math.floor(turns_index(float(scaling["fast"]))), 0)
+    high = min(math.ceil(turns_index(float(scaling["slow"]))), dims - 1)
+    ramp = np.clip((np.arange(half, dtype=np.float64) - low) / max(high - low, 0.001), 0.0, 1.0)
+    return plain / factor * ramp + plain * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+@POSITION_ENCODINGS.register("rotary_blend")
+class RotaryBlend(PositionEncoding):
+    """Rotate-half rotation of a head's first ``dims`` numbers (number ``i`` with number ``i + dims / 2``) by
+    ``position * f_i``, the frequencies blended between plain and stretched ones and the amplitude raised with the
+    stretch (:func:`blended_inverse_frequencies`); the rest of the head passes unchanged.
+
+    params: ``head_dim``, ``dims`` (even, at most ``head_dim``), ``base``, ``scaling`` (mapping with ``factor``,
+    ``original``, ``fast``, ``slow``, or None).  The frequencies are taken in 64-bit on the host and rounded once to
+    32-bit; the angle and its sine and cosine are 32-bit, in the kernel that applies them (the mixer's
+    rotate-normalise-and-store kernel reads ``half_inv_freq``, ``amplitude`` and ``dims``)."""
+
+    def __init__(self, spec: PartSpec, tensors, runtime: Runtime):
+        super().__init__(spec, tensors, runtime)
+        params = spec.params
+        self.head_dim = int(params["head_dim"])
+        self.dims = int(params["dims"])
+        self.base = float(params["base"])
+        if self.dims < 0 or self.dims % 2 or self.dims > self.head_dim:
+            raise ValueError(f"rotation of halves needs an even number of dimensions up to {self.head_dim}, got {self.dims}")
+        if not self.base > 0.0 or self.base == 1.0:
+            raise ValueError("the rotation's base must be positive and not 1")
+        scaling = params.get("scaling")
+        frequencies, self.amplitude = blended_inverse_frequencies(self.dims, self.base, dict(scaling) if scaling else None)
+        self.inv_freq_host = frequencies.astype(np.float32)
+        self.half_inv_freq = torch.from_numpy(self.inv_freq_host).to(runtime.device) if self.dims else None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        raise NotImplementedError("the rotation of halves is applied by the mixer's rotate-normalise-and-store kernel")
+
+
 @POSITION_ENCODINGS.register("none")
 class NoPositionEncoding(PositionEncoding):
     """Leaves queries and keys as they are."""
