@@ -3,6 +3,7 @@
 //
 //   tb_route_topk      z = W_r h in 32-bit (a K-ordered slice per lane, then a fixed butterfly); the `top` largest
 //                      z of a row, largest first (the lowest index wins a tie), and the softmax over those alone.
+//   tb_choose_topk     the same choice from logits that a 32-bit product kernel has already left.
 //   tb_expert_plan     rows * top assignments (row t, slot s -> assignment t * top + s) are grouped by their expert:
 //                      offsets[e] .. offsets[e + 1] of `order` name the assignments of expert e.
 //   tb_expert_linear   out[a, :] = act(W[expert(a)] in[source(a), :]) for every assignment a, a tile of one expert's
@@ -22,76 +23,81 @@ namespace {
 
 constexpr int kRouteWarps = 4;
 
-// R rows a warp: a weight is loaded once for all of them.  The arithmetic of a row is the same for every R.
-template <typename T, int R>
+// The `top` largest of a row's logits `z` (the warp's own copy in shared memory, consumed here), largest first, the
+// lowest index winning a tie, and the softmax over those alone.
+__device__ __forceinline__ void choose_top(float* z, int experts, int top, int* __restrict__ ids,
+                                           float* __restrict__ weights, int lane) {
+    float first = 0.0f, total = 0.0f;
+    for (int s = 0; s < top; ++s) {
+        float best = -INFINITY;
+        int where = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float v = z[e];
+            if (v > best) { best = v; where = e; }              // (ascending e: the lowest index of equal values stays)
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int ow = __shfl_xor_sync(0xffffffffu, where, o);
+            if (ob > best || (ob == best && ow < where)) { best = ob; where = ow; }
+        }
+        if (where == 0x7fffffff) where = 0;                      // (only if every logit is NaN or -inf)
+        if (s == 0) first = best;
+        const float p = expf(best - first);
+        total += p;
+        if (lane == 0) {
+            ids[s] = where;
+            weights[s] = p;
+            z[where] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    const float inv = 1.0f / total;
+    for (int s = lane; s < top; s += 32) weights[s] *= inv;      // (lane 0's stores above are visible: same warp, synced)
+}
+
+// A warp a row: the row in shared memory, a K-strided slice per lane and expert, a fixed butterfly.  For steps of few
+// rows; steps of many rows take their logits from the 32-bit product kernel and only choose here.
+template <typename T>
 __global__ void __launch_bounds__(kRouteWarps * 32)
 route_topk_kernel(const T* __restrict__ x, int64_t x_stride, const float* __restrict__ router, int* __restrict__ ids,
                   float* __restrict__ weights, int rows, int width, int experts, int top) {
-    extern __shared__ __align__(16) float route_smem[];          // per warp: R rows of `width`, then R * experts logits
+    extern __shared__ __align__(16) float route_smem[];          // per warp: the row, then its logits
     pdl_trigger();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = (blockIdx.x * kRouteWarps + warp) * R;
-    if (row0 >= rows) return;                                    // the whole warp leaves; no block-wide barrier below
-    float* xs = route_smem + (size_t)warp * R * (width + experts);
-    float* zs = xs + (size_t)R * width;
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int row = min(row0 + r, rows - 1);
-        const T* xr = x + (int64_t)row * x_stride;
-        for (int i = lane; i < width; i += 32) xs[r * width + i] = Elem<T>::load(xr + i);
-    }
+    const int row = blockIdx.x * kRouteWarps + warp;
+    if (row >= rows) return;                                     // the whole warp leaves; no block-wide barrier below
+    float* xs = route_smem + (size_t)warp * (width + experts);
+    float* zs = xs + width;
+    const T* xr = x + (int64_t)row * x_stride;
+    for (int i = lane; i < width; i += 32) xs[i] = Elem<T>::load(xr + i);
     __syncwarp();
     for (int e = 0; e < experts; ++e) {
         const float* w = router + (int64_t)e * width;
-        float dot[R];
-#pragma unroll
-        for (int r = 0; r < R; ++r) dot[r] = 0.0f;
-        for (int i = lane; i < width; i += 32) {
-            const float wv = w[i];
-#pragma unroll
-            for (int r = 0; r < R; ++r) dot[r] = fmaf(xs[r * width + i], wv, dot[r]);
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const float z = warp_sum(dot[r]);
-            if (lane == 0) zs[r * experts + e] = z;
-        }
+        float dot = 0.0f;
+        for (int i = lane; i < width; i += 32) dot = fmaf(xs[i], w[i], dot);
+        dot = warp_sum(dot);
+        if (lane == 0) zs[e] = dot;
     }
     __syncwarp();
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int row = row0 + r;
-        if (row >= rows) break;
-        float* z = zs + r * experts;
-        float first = 0.0f, total = 0.0f;
-        for (int s = 0; s < top; ++s) {
-            float best = -INFINITY;
-            int where = 0x7fffffff;
-            for (int e = lane; e < experts; e += 32) {
-                const float v = z[e];
-                if (v > best) { best = v; where = e; }          // (ascending e: the lowest index of equal values stays)
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const int ow = __shfl_xor_sync(0xffffffffu, where, o);
-                if (ob > best || (ob == best && ow < where)) { best = ob; where = ow; }
-            }
-            if (where == 0x7fffffff) where = 0;                  // (only if every logit is NaN or -inf)
-            if (s == 0) first = best;
-            const float p = expf(best - first);
-            total += p;
-            if (lane == 0) {
-                ids[(int64_t)row * top + s] = where;
-                weights[(int64_t)row * top + s] = p;
-                z[where] = -INFINITY;
-            }
-            __syncwarp();
-        }
-        const float inv = 1.0f / total;
-        for (int s = lane; s < top; s += 32) weights[(int64_t)row * top + s] *= inv;     // (lane 0's stores above are visible: same warp, synced)
-    }
+    choose_top(zs, experts, top, ids + (int64_t)row * top, weights + (int64_t)row * top, lane);
+}
+
+// The choice alone, from logits that a product kernel left: logits 32-bit [rows, experts].
+__global__ void __launch_bounds__(kRouteWarps * 32)
+choose_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights, int rows,
+                   int experts, int top) {
+    extern __shared__ __align__(16) float route_smem[];          // per warp: its row's logits
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kRouteWarps + warp;
+    if (row >= rows) return;
+    float* zs = route_smem + (size_t)warp * experts;
+    for (int e = lane; e < experts; e += 32) zs[e] = logits[(int64_t)row * experts + e];
+    __syncwarp();
+    choose_top(zs, experts, top, ids + (int64_t)row * top, weights + (int64_t)row * top, lane);
 }
 
 // ----------------------------------------------------------------------------- grouping
@@ -380,14 +386,13 @@ TB_EXPORT int tb_route_topk(const void* x, int64_t x_stride, const float* router
                             int width, int experts, int top, int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
     if (width < 1 || experts < 1 || top < 1 || top > experts) return TB_ERR_BAD_SIZE;
-    const int per_warp = rows >= 512 ? 4 : 1;
-    const size_t smem = (size_t)kRouteWarps * per_warp * (width + experts) * sizeof(float);
+    const size_t smem = (size_t)kRouteWarps * (width + experts) * sizeof(float);
     if (smem > 200 * 1024) return TB_ERR_BAD_SIZE;
-    const dim3 grid((rows + kRouteWarps * per_warp - 1) / (kRouteWarps * per_warp));
+    const dim3 grid((rows + kRouteWarps - 1) / kRouteWarps);
     cudaError_t launched;
-#define TB_ROUTE(T, R)                                                                                              \
+#define TB_ROUTE(T)                                                                                                 \
     do {                                                                                                            \
-        auto kernel = route_topk_kernel<T, R>;                                                                      \
+        auto kernel = route_topk_kernel<T>;                                                                         \
         if (smem > 40 * 1024) {                                                                                     \
             cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (err != cudaSuccess) return (int)err;                                                                \
@@ -395,14 +400,22 @@ TB_EXPORT int tb_route_topk(const void* x, int64_t x_stride, const float* router
         launched = tb_launch_pdl(kernel, grid, dim3(kRouteWarps * 32), smem, stream, (const T*)x, x_stride, router, \
                                  ids, weights, rows, width, experts, top);                                          \
     } while (0)
-    if (dtype == TB_F32) {
-        if (per_warp == 4) TB_ROUTE(float, 4); else TB_ROUTE(float, 1);
-    } else if (dtype == TB_BF16) {
-        if (per_warp == 4) TB_ROUTE(__nv_bfloat16, 4); else TB_ROUTE(__nv_bfloat16, 1);
-    } else {
-        return TB_ERR_BAD_DTYPE;
-    }
+    if (dtype == TB_F32) TB_ROUTE(float);
+    else if (dtype == TB_BF16) TB_ROUTE(__nv_bfloat16);
+    else return TB_ERR_BAD_DTYPE;
 #undef TB_ROUTE
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
+// logits: 32-bit [rows, experts], contiguous.
+TB_EXPORT int tb_choose_topk(const float* logits, int* ids, float* weights, int rows, int experts, int top,
+                             cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (experts < 1 || top < 1 || top > experts) return TB_ERR_BAD_SIZE;
+    const size_t smem = (size_t)kRouteWarps * experts * sizeof(float);
+    if (smem > 40 * 1024) return TB_ERR_BAD_SIZE;
+    cudaError_t launched = tb_launch_pdl(choose_topk_kernel, dim3((rows + kRouteWarps - 1) / kRouteWarps),
+                                         dim3(kRouteWarps * 32), smem, stream, logits, ids, weights, rows, experts, top);
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 

@@ -59,7 +59,8 @@ def check_upload(model: DecoderModel, model_dir: str) -> str:
     from ..weights.safetensors_io import SafetensorsSource
 
     name = model.spec.final_norm.weights.get("weight")
-    on_device = getattr(model.final_norm, "weight", None)
+    # (a norm that adds an offset to its stored weight keeps the stored values beside the sum)
+    on_device = getattr(model.final_norm, "checkpoint_weight", getattr(model.final_norm, "weight", None))
     if name is None or on_device is None:
         raise RuntimeError("the model's final norm holds no weight to check")
     stored = SafetensorsSource(model_dir).tensor(name)

@@ -1019,6 +1019,34 @@ def route_topk(x: torch.Tensor, router: torch.Tensor, ids: torch.Tensor, weights
                              _i32(router.shape[0]), _i32(top), _i32(_code(x.dtype)), _stream()), "route_topk")
 
 
+ROUTE_FUSED_MAX_ROWS = 256     # up to here the router's product and the choice are one kernel, a warp a row
+
+
+def widen_rows(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = float32(x)`` for bfloat16 rows ``x`` (row stride free) and a contiguous float32 ``out``."""
+    _cuda(x, out)
+    _need(x.dtype == torch.bfloat16 and x.stride(1) == 1 and out.dtype == torch.float32 and out.is_contiguous()
+          and out.shape == x.shape, "widen_rows x/out")
+    lib = load_library("pointwise")
+    _check(lib.tb_widen_rows(_ptr(x), _i64(x.stride(0)), _ptr(out), _i32(x.shape[0]), _i32(x.shape[1]), _stream()),
+           "widen_rows")
+    return out
+
+
+def choose_topk(logits: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """The ``top`` largest of every row of ``logits`` (float32 ``[T, E]``; largest first) into ``ids`` and the softmax
+    over those into ``weights``: :func:`route_topk` without the router's product."""
+    _cuda(logits, ids, weights)
+    rows, experts = logits.shape
+    top = ids.shape[1]
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "choose_topk logits")
+    _need(ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (rows, top), "choose_topk ids")
+    _need(weights.dtype == torch.float32 and weights.is_contiguous() and weights.shape == (rows, top), "choose_topk weights")
+    lib = load_library("experts")
+    _check(lib.tb_choose_topk(_ptr(logits), _ptr(ids), _ptr(weights), _i32(rows), _i32(experts), _i32(top), _stream()),
+           "choose_topk")
+
+
 def expert_plan(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: torch.Tensor) -> None:
     """Group the assignments ``ids.flatten()`` by expert: ``order[offsets[e] : offsets[e + 1]]`` are expert ``e``'s."""
     _cuda(ids, offsets, order)

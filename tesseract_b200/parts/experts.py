@@ -86,7 +86,14 @@ class RoutedExperts(FeedForward):
         rows = x.shape[0]
         ids = torch.empty((rows, self.top_k), dtype=torch.int32, device=x.device)
         weights = torch.empty((rows, self.top_k), dtype=torch.float32, device=x.device)
-        kernels.route_topk(x, self.router, ids, weights)
+        if rows <= kernels.ROUTE_FUSED_MAX_ROWS:
+            kernels.route_topk(x, self.router, ids, weights)
+            return ids, weights
+        # many rows: the logits through the package's 32-bit product (operands widened exactly), then the choice
+        wide = x if x.dtype == torch.float32 else kernels.widen_rows(x, torch.empty(x.shape, dtype=torch.float32, device=x.device))
+        logits = torch.empty((rows, self.num_experts), dtype=torch.float32, device=x.device)
+        kernels.gemm_f32_nt(wide.contiguous() if not wide.is_contiguous() else wide, self.router, logits)
+        kernels.choose_topk(logits, ids, weights)
         return ids, weights
 
     def forward(self, x, ctx: StepContext, follow=None):

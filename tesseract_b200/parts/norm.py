@@ -79,6 +79,7 @@ class GroupedRMSNorm(Norm):
         self.offset = float(params.get("offset") or 0.0)
         self.weight = runtime.vector_f32(tensors["weight"])
         if self.offset:
+            self.checkpoint_weight = self.weight          # as stored (what an upload check compares)
             self.weight = self.weight + self.offset
 
     @classmethod

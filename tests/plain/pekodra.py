@@ -138,9 +138,25 @@ def route(h: torch.Tensor, router: torch.Tensor, top: int):
     return chosen, torch.softmax(values, dim=-1)
 
 
-def expert_mixture(h: torch.Tensor, w: Mapping[str, torch.Tensor], mlp: Mapping) -> torch.Tensor:
+def expert_mixture(h: torch.Tensor, w: Mapping[str, torch.Tensor], mlp: Mapping, chosen: Optional[torch.Tensor] = None,
+                   report: Optional[list] = None) -> torch.Tensor:
+    """``chosen`` (``[T, top]``) overrides the router's choice (the weights are still the softmax over the chosen
+    logits): a comparison with an implementation in lower precision then does not hang on which of two nearly equal
+    logits it found larger.  ``report`` receives ``(own choice [T, top], margin [T])``, the margin being the distance
+    between the last chosen and the first rejected logit over the spread of the row's logits."""
     experts, top = mlp["router"]["experts"], mlp["router"]["top"]
-    chosen, weights = route(h, w["router"], top)
+    own, weights = route(h, w["router"], top)
+    if report is not None or chosen is not None:
+        logits = h @ w["router"].T
+        ranked = torch.sort(logits, dim=-1, descending=True).values
+        margin = (ranked[:, top - 1] - ranked[:, top]) if top < experts else torch.full((h.shape[0],), float("inf"))
+        if report is not None:
+            report.append((own, margin / (logits.std(dim=-1) + 1e-30)))
+        if chosen is not None:
+            chosen = chosen.long()
+            weights = torch.softmax(torch.gather(logits, 1, chosen), dim=-1)
+    if chosen is None:
+        chosen = own
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for slot in range(top):
@@ -172,8 +188,12 @@ def _sub(tensors: Mapping[str, torch.Tensor], prefix: str, dtype) -> Dict[str, t
 
 
 def forward(config: Mapping, tensors: Mapping[str, torch.Tensor], tokens: Sequence[int], dtype=torch.float64,
-            keep_layers: bool = False):
-    """Logits ``[T, vocab]`` of a whole sequence (and, with ``keep_layers``, the stream after every layer run)."""
+            keep_layers: bool = False, routing: Optional[Mapping[int, torch.Tensor]] = None,
+            report: Optional[list] = None):
+    """Logits ``[T, vocab]`` of a whole sequence (and, with ``keep_layers``, the stream after every layer run).
+    ``routing[n]`` (``[T, top]``) fixes the experts of the n-th run of a layer with experts; ``report`` receives the
+    model's own choice and its margin for every such run (see :func:`expert_mixture`)."""
+    routed_runs = 0
     eps = float(config["norm"]["eps"])
     x0 = tensors["embed"].to(dtype)[list(tokens)] * float(config["embedding"]["scale"])
     x = x0
@@ -189,7 +209,11 @@ def forward(config: Mapping, tensors: Mapping[str, torch.Tensor], tokens: Sequen
         if mlp:
             h2 = offset_rms_norm(x, tensors[prefix + "norm2"].to(dtype), eps)
             w = _sub(tensors, prefix + "mlp.", dtype)
-            fed = gated_mlp(h2, w) if mlp["kind"] == "dense" else expert_mixture(h2, w, mlp)
+            if mlp["kind"] == "dense":
+                fed = gated_mlp(h2, w)
+            else:
+                fed = expert_mixture(h2, w, mlp, None if routing is None else routing[routed_runs], report)
+                routed_runs += 1
             x = x + (mixed + fed)
         else:
             x = x + mixed
