@@ -664,8 +664,8 @@ def run_kernels(args):
 
 
 # ----------------------------------------------------------------------------- another design beside Llama
-# `--design revesun`: prefill and decode of a Revesun model at layer sizes like a real model's (random weights),
-# beside a Llama of the same width, heads, head sizes, layer count and about as many weights a layer, measured the
+# `--design revesun|pekodra`: prefill and decode of a model of that design at layer sizes like a real model's (random
+# weights), beside a Llama (and, for Pekodra, a Revesun: the other design with a 32-bit stream) of the same width, heads, head sizes, layer count and about as many weights a layer, measured the
 # same way; then the design's own kernels alone, against the bytes they must move.  The default workload is untouched.
 DESIGN_SIZES = {
     "1b": dict(width=2048, heads=32, kv_heads=8, dim=64, layers=16, llama_ff=8192, dense_ff=12288, block=128, taps=4,
@@ -689,6 +689,36 @@ def revesun_config(size, layers):
     return {"architecture": "Revesun", "torch_dtype": "bfloat16", "width": z["width"], "vocab": DESIGN_VOCAB,
             "norm": {"eps": 1e-5, "groups": z["groups"]},
             "layers": [recurrent if i % 4 == 3 else attention for i in range(layers)]}
+
+
+PEKODRA_SIZES = {
+    # (the layers run: `layers` of them, the middle `looped` walked twice, is as many as the Llama beside it has)
+    "1b": dict(window=512, rot_dims=64, dense_ff=8192, experts=32, top=4, expert_ff=1024, shared_ff=2048, stored=10, looped=(2, 8)),
+    "3b": dict(window=512, rot_dims=64, dense_ff=8192, experts=32, top=4, expert_ff=1024, shared_ff=2048, stored=8, looped=(2, 6)),
+    "8b": dict(window=512, rot_dims=128, dense_ff=14336, experts=32, top=4, expert_ff=2048, shared_ff=4096, stored=5, looped=(1, 4)),
+}
+
+
+def pekodra_config(size, layers):
+    """Layers alternate between a dense feed-forward and routed experts; a run in the middle is walked twice, so that
+    `layers` layer runs happen in all (as many as the models beside it run)."""
+    z, p = DESIGN_SIZES[size], PEKODRA_SIZES[size]
+    stored, (start, stop) = p["stored"], p["looped"]
+    if layers != z["layers"]:                      # another layer count: no loop, one stored layer a run
+        stored, start, stop = layers, 0, 0
+    mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+             "mask": {"size": p["window"]}, "scale": z["dim"] ** -0.5,
+             "rot": {"dims": p["rot_dims"], "base": 1000000.0,
+                     "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    dense = {"kind": "dense", "ff": p["dense_ff"]}
+    moe = {"kind": "moe", "router": {"experts": p["experts"], "top": p["top"]}, "expert": {"ff": p["expert_ff"]},
+           "shared": {"ff": p["shared_ff"]}}
+    config = {"architecture": "Pekodra", "torch_dtype": "bfloat16", "width": z["width"], "vocab": DESIGN_VOCAB,
+              "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_scale": 1.0,
+              "layers": [{"type": "attention", "mixer": mixer, "mlp": moe if i % 2 else dense} for i in range(stored)]}
+    if stop > start:
+        config["loop"] = {"start": start, "stop": stop, "times": 2}
+    return config
 
 
 def run_design(args):
@@ -773,11 +803,15 @@ def run_design(args):
         scratch.cleanup()
         return out
 
-    result = {"design": "Revesun", "size": args.size, "layers": layers, "vocab": DESIGN_VOCAB, "dtype": "bf16",
-              "data": "synthetic", "l2": "a 256 MB buffer is written between timed prefill steps; a decode step "
-                                         "reads its weights, which exceed L2",
-              "revesun": measure(revesun_config(args.size, layers)), "llama": measure(llama)}
-    result["kernels"] = design_kernels(args.size, pk)
+    result = {"design": {"revesun": "Revesun", "pekodra": "Pekodra"}[args.design], "size": args.size, "layers": layers,
+              "vocab": DESIGN_VOCAB, "dtype": "bf16", "data": "synthetic",
+              "l2": "a 256 MB buffer is written between timed prefill steps; a decode step reads its weights, which "
+                    "exceed L2"}
+    if args.design == "pekodra":
+        result["pekodra"] = measure(pekodra_config(args.size, layers))
+    result["revesun"] = measure(revesun_config(args.size, layers))
+    result["llama"] = measure(llama)
+    result["kernels"] = pekodra_kernels(args.size, pk) if args.design == "pekodra" else design_kernels(args.size, pk)
     result["clocks"] = sampler.stop(windows)
     result["peaks"] = pk
     print(json.dumps(result))
@@ -895,6 +929,166 @@ def design_kernels(size, pk):
     return out
 
 
+def pekodra_kernels(size, pk):
+    """Pekodra's own kernels alone at this size, timed like :func:`design_kernels`: 2,048 prompt rows of one sequence,
+    and 64 decoded rows at context 2,048."""
+    import torch
+
+    from tesseract_b200 import kernels
+    from tesseract_b200.parts.rotary import blended_inverse_frequencies
+
+    z, p = DESIGN_SIZES[size], PEKODRA_SIZES[size]
+    dev = "cuda"
+    H, G, d, W = z["heads"], z["kv_heads"], z["dim"], z["width"]
+    F, E, top, EF, window, page = p["dense_ff"], p["experts"], p["top"], p["expert_ff"], p["window"], PAGE_SIZE
+    channels = H * d + 2 * G * d
+    freqs, amplitude = blended_inverse_frequencies(p["rot_dims"], 1e6, {"factor": 4.0, "original": 2048, "fast": 32.0,
+                                                                       "slow": 1.0})
+    inv_freq = torch.tensor(freqs, dtype=torch.float32, device=dev)
+    SETS = 8
+    out = {}
+
+    def timed(name, make, nbytes, flops=0, tensor=False):
+        runs = [make(k) for k in range(SETS)]
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for run in runs:
+                run()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()                 # one graph of the eight launches: no host time between them
+        with torch.cuda.graph(graph):
+            for run in runs:
+                run()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3 / SETS)
+        us = statistics.median(times)
+        line = {"us": round(us, 2), "mb": round(nbytes / 1e6, 2), "gbs": round(nbytes / us / 1e3, 1),
+                "frac_of_measured_hbm": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+        if flops:
+            line["tflops"] = round(flops / us / 1e6, 2)
+            if tensor:
+                line["frac_of_measured_bf16"] = round(flops / us / 1e6 / pk["bf16_tflops"], 4)
+        out[name] = line
+
+    for label, rows, seqs, begin in (("prefill_2048", 2048, 1, 0), ("decode_64", 64, 64, 2047)):
+        new = rows // seqs
+        positions = (torch.arange(rows, dtype=torch.int32, device=dev) % new) + begin
+        seq_of_row = torch.arange(rows, dtype=torch.int32, device=dev) // new
+        pages_per_seq = 2048 // page
+        table = (torch.arange(seqs * pages_per_seq, dtype=torch.int32, device=dev) + 1).view(seqs, pages_per_seq)
+        page_elems = G * page * 2 * d
+
+        def norms(k):
+            res, a, b = (torch.randn(rows, W, device=dev) for _ in range(3))
+            w1, w2 = torch.ones(W, device=dev), torch.ones(W, device=dev)
+            y1 = torch.empty(rows, W, dtype=torch.bfloat16, device=dev)
+            y2 = torch.empty_like(y1)
+            return lambda: kernels.sum_norms(res, a, b, w1, y1, w2, y2, 1e-6)
+
+        timed(f"sum_norms (two updates, two norms)/{label}", norms, rows * W * (4 * 4 + 2 * 2))
+
+        def concat(k):
+            res, a, b, origin = (torch.randn(rows, W, device=dev) for _ in range(4))
+            y = torch.empty(rows, 2 * W, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.sum_concat(res, a, b, origin, y)
+
+        timed(f"sum_concat/{label}", concat, rows * W * (4 * 4 + 2 * 2))
+
+        def rotate(k):
+            proj = torch.randn(rows, channels, device=dev).bfloat16()
+            q = torch.empty(rows, H * d, dtype=torch.bfloat16, device=dev)
+            cache = torch.zeros(seqs * pages_per_seq + 1, page_elems, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.rope_norm_cache(proj, q, cache, positions, seq_of_row, table, inv_freq,
+                                                   amplitude=amplitude, heads=H, kv_heads=G, dim=d, vdim=d,
+                                                   rot_dims=p["rot_dims"], unit_norm=True, eps=1e-6, page_size=page)
+
+        timed(f"rope_norm_cache/{label}", rotate, rows * channels * 2 * 2)
+
+        def attend(k):
+            q = torch.randn(rows, H * d, device=dev).bfloat16()
+            o = torch.empty(rows, H * d, dtype=torch.bfloat16, device=dev)
+            cache = torch.randn(seqs * pages_per_seq + 1, page_elems, device=dev).bfloat16()
+            return lambda: kernels.attention_masked(q, None, o, cache, positions, seq_of_row, table, heads=H, kv_heads=G,
+                                                    dim=d, vdim=d, page_size=page, mask_kind=kernels.MASK_WINDOW,
+                                                    mask_size=window, sink=False, scale=d ** -0.5)
+
+        keys_seen = sum(min(int(q), window - 1) + 1 for q in positions.tolist())
+        kv_read = (2048 if new > 1 else seqs * min(begin + 1, window)) * G * 2 * d * 2
+        timed(f"attention_masked (window {window})/{label}", attend, rows * H * d * 2 * 2 + kv_read,
+              flops=keys_seen * H * 2 * d * 2)
+
+        def act(k):
+            gu = torch.randn(rows, 2 * F, device=dev).bfloat16()
+            bias = torch.randn(2 * F, device=dev)
+            y = torch.empty(rows, F, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.gated_activation(gu, bias, y, kernels.ACT_GELU_TANH)
+
+        timed(f"gated_activation (tanh-GELU, biases)/{label}", act, rows * F * 2 * 3)
+
+        def route(k):
+            x = torch.randn(rows, W, device=dev).bfloat16()
+            router = torch.randn(E, W, device=dev)
+            ids = torch.empty(rows, top, dtype=torch.int32, device=dev)
+            weights = torch.empty(rows, top, dtype=torch.float32, device=dev)
+            if rows <= kernels.ROUTE_FUSED_MAX_ROWS:
+                return lambda: kernels.route_topk(x, router, ids, weights)
+            wide = torch.empty(rows, W, device=dev)
+            logits = torch.empty(rows, E, device=dev)
+
+            def run():
+                kernels.widen_rows(x, wide)
+                kernels.gemm_f32_nt(wide, router, logits)
+                kernels.choose_topk(logits, ids, weights)
+            return run
+
+        timed(f"router (32-bit product, choice)/{label}", route, rows * W * 2 + E * W * 4, flops=rows * E * W * 2)
+
+        ids = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(rows)]).to(torch.int32).contiguous()
+        offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        order = torch.empty(rows * top, dtype=torch.int32, device=dev)
+        kernels.expert_plan(ids, E, offsets, order)
+        timed(f"expert_plan/{label}", lambda k: (lambda: kernels.expert_plan(ids, E, offsets, order)), rows * top * 8)
+        used = min(E, rows * top)                      # experts whose weights a step must read
+
+        def experts_up(k):
+            x = torch.randn(rows, W, device=dev).bfloat16()
+            up = torch.randn(E, EF, W, device=dev).bfloat16()
+            hidden = torch.empty(rows * top, EF, dtype=torch.bfloat16, device=dev)
+            return lambda: kernels.expert_linear(x, up, hidden, offsets, order, source_div=top,
+                                                 epilogue=kernels.EXPERT_SQUARED_RELU)
+
+        timed(f"expert_linear up + squared ReLU/{label}", experts_up, used * EF * W * 2 + rows * W * 2 + rows * top * EF * 2,
+              flops=rows * top * EF * W * 2, tensor=True)
+
+        def experts_down(k):
+            hidden = torch.randn(rows * top, EF, device=dev).bfloat16()
+            down = torch.randn(E, W, EF, device=dev).bfloat16()
+            parts = torch.empty(rows * top, W, device=dev)
+            return lambda: kernels.expert_linear(hidden, down, parts, offsets, order, source_div=1)
+
+        timed(f"expert_linear down/{label}", experts_down, used * EF * W * 2 + rows * top * (EF * 2 + W * 4),
+              flops=rows * top * EF * W * 2, tensor=True)
+
+        def combine(k):
+            parts = torch.randn(rows * top, W, device=dev)
+            weights = torch.rand(rows, top, device=dev)
+            base = torch.randn(rows, W, device=dev)
+            return lambda: kernels.expert_combine(parts, weights, base, base)
+
+        timed(f"expert_combine/{label}", combine, rows * W * 4 * (top + 2))
+    return out
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -916,7 +1110,7 @@ def main():
     parser.add_argument("--workload", choices=["3b", "8b"], default=None,
                         help="run another workload instead of the headline one: continuous batching at the 3B sizes, "
                              "or a 2,048-token portion beside 64 decode rows at the 8B sizes")
-    parser.add_argument("--design", choices=["revesun"], default=None,
+    parser.add_argument("--design", choices=["revesun", "pekodra"], default=None,
                         help="instead of the headline workload: prefill and decode of this design beside a Llama of "
                              "equal layer sizes (--size), and the design's own kernels alone")
     args = parser.parse_args()
