@@ -1036,22 +1036,16 @@ def pekodra_kernels(size, pk):
         timed(f"gated_activation (tanh-GELU, biases)/{label}", act, rows * F * 2 * 3)
 
         def route(k):
+            from tesseract_b200.parts import Runtime
+            from tesseract_b200.parts.linear import Linear
+
             x = torch.randn(rows, W, device=dev).bfloat16()
-            router = torch.randn(E, W, device=dev)
+            router = Linear(torch.randn(E, W).bfloat16(), Runtime(torch.bfloat16, torch.device(dev)))
             ids = torch.empty(rows, top, dtype=torch.int32, device=dev)
             weights = torch.empty(rows, top, dtype=torch.float32, device=dev)
-            if rows <= kernels.ROUTE_FUSED_MAX_ROWS:
-                return lambda: kernels.route_topk(x, router, ids, weights)
-            wide = torch.empty(rows, W, device=dev)
-            logits = torch.empty(rows, E, device=dev)
+            return lambda: kernels.choose_topk(router.forward(x, float32_out=True), ids, weights)
 
-            def run():
-                kernels.widen_rows(x, wide)
-                kernels.gemm_f32_nt(wide, router, logits)
-                kernels.choose_topk(logits, ids, weights)
-            return run
-
-        timed(f"router (32-bit product, choice)/{label}", route, rows * W * 2 + E * W * 4, flops=rows * E * W * 2)
+        timed(f"router (product with 32-bit logits, choice)/{label}", route, rows * W * 2 + E * W * 2, flops=rows * E * W * 2)
 
         ids = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(rows)]).to(torch.int32).contiguous()
         offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)

@@ -1,9 +1,8 @@
 // A feed-forward made of many small experts of which every row takes a few: the router, the grouping of rows by
 // expert, the experts' products, and the weighted sum.
 //
-//   tb_route_topk      z = W_r h in 32-bit (a K-ordered slice per lane, then a fixed butterfly); the `top` largest
-//                      z of a row, largest first (the lowest index wins a tie), and the softmax over those alone.
-//   tb_choose_topk     the same choice from logits that a 32-bit product kernel has already left.
+//   tb_choose_topk     from the router's 32-bit logits (a product kernel left them): the `top` largest of a row,
+//                      largest first (the lowest index wins a tie), and the softmax over those alone.
 //   tb_expert_plan     rows * top assignments (row t, slot s -> assignment t * top + s) are grouped by their expert:
 //                      offsets[e] .. offsets[e + 1] of `order` name the assignments of expert e.
 //   tb_expert_linear   out[a, :] = act(W[expert(a)] in[source(a), :]) for every assignment a, a tile of one expert's
@@ -56,35 +55,7 @@ __device__ __forceinline__ void choose_top(float* z, int experts, int top, int* 
     for (int s = lane; s < top; s += 32) weights[s] *= inv;      // (lane 0's stores above are visible: same warp, synced)
 }
 
-// A warp a row: the row in shared memory, a K-strided slice per lane and expert, a fixed butterfly.  For steps of few
-// rows; steps of many rows take their logits from the 32-bit product kernel and only choose here.
-template <typename T>
-__global__ void __launch_bounds__(kRouteWarps * 32)
-route_topk_kernel(const T* __restrict__ x, int64_t x_stride, const float* __restrict__ router, int* __restrict__ ids,
-                  float* __restrict__ weights, int rows, int width, int experts, int top) {
-    extern __shared__ __align__(16) float route_smem[];          // per warp: the row, then its logits
-    pdl_trigger();
-    pdl_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * kRouteWarps + warp;
-    if (row >= rows) return;                                     // the whole warp leaves; no block-wide barrier below
-    float* xs = route_smem + (size_t)warp * (width + experts);
-    float* zs = xs + width;
-    const T* xr = x + (int64_t)row * x_stride;
-    for (int i = lane; i < width; i += 32) xs[i] = Elem<T>::load(xr + i);
-    __syncwarp();
-    for (int e = 0; e < experts; ++e) {
-        const float* w = router + (int64_t)e * width;
-        float dot = 0.0f;
-        for (int i = lane; i < width; i += 32) dot = fmaf(xs[i], w[i], dot);
-        dot = warp_sum(dot);
-        if (lane == 0) zs[e] = dot;
-    }
-    __syncwarp();
-    choose_top(zs, experts, top, ids + (int64_t)row * top, weights + (int64_t)row * top, lane);
-}
-
-// The choice alone, from logits that a product kernel left: logits 32-bit [rows, experts].
+// A warp a row; logits 32-bit [rows, experts].
 __global__ void __launch_bounds__(kRouteWarps * 32)
 choose_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights, int rows,
                    int experts, int top) {
@@ -328,6 +299,133 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ in, int64_t in_stride
     }
 }
 
+// The same product for K a multiple of 64: a block of eight warps takes 64 assignments by 128 features (a warp 32 by
+// 32); K runs in steps of 64 through a ring of three stages that cp.async fills two steps ahead (rows of absent
+// assignments and features are zero-filled), fragments come from shared memory by ldmatrix, 16-byte chunks of a row
+// XOR-swizzled by the row so that neither the copies nor ldmatrix meet bank conflicts.
+constexpr int PM = 64, PN = 128, PK = 64, PSTAGES = 3;
+constexpr int kPipeSmem = PSTAGES * (PM + PN) * PK * 2;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a tile whose rows are 128 bytes
+__device__ __forceinline__ uint32_t swizzled(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+template <typename O, int EPI>
+__global__ void __launch_bounds__(256)
+expert_linear_pipe_kernel(const __nv_bfloat16* __restrict__ in, int64_t in_stride, const __nv_bfloat16* __restrict__ W,
+                          O* __restrict__ out, int64_t out_stride, const int* __restrict__ offsets,
+                          const int* __restrict__ order, int experts, int top_div, int N, int K) {
+    extern __shared__ __align__(128) unsigned char pipe_smem[];
+    __shared__ int rows_of[PM];
+    pdl_trigger();
+    pdl_wait();
+    int expert, first, count;
+    if (!find_tile(offsets, experts, blockIdx.y, PM, expert, first, count)) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < PM) rows_of[tid] = tid < count ? order[first + tid] : -1;
+    __syncthreads();
+    const __nv_bfloat16* We = W + (int64_t)expert * N * K;
+    const int n0 = blockIdx.x * PN;
+    const uint32_t base = (uint32_t)__cvta_generic_to_shared(pipe_smem);
+    // what this thread copies every step: two chunks of A (64 rows x 8 chunks) and four of W (128 rows x 8 chunks)
+    const __nv_bfloat16* a_src[2];
+    uint32_t a_dst[2];
+    int a_bytes[2];
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+        const int c = tid + p * 256, r = c >> 3, chunk = c & 7;
+        const int a = rows_of[r];
+        a_bytes[p] = a < 0 ? 0 : 16;
+        a_src[p] = in + (a < 0 ? 0 : (int64_t)(a / top_div) * in_stride) + chunk * 8;
+        a_dst[p] = swizzled(r, chunk);
+    }
+    const __nv_bfloat16* w_src[4];
+    uint32_t w_dst[4];
+    int w_bytes[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const int c = tid + p * 256, r = c >> 3, chunk = c & 7;
+        const int n = n0 + r;
+        w_bytes[p] = n < N ? 16 : 0;
+        w_src[p] = We + (n < N ? (int64_t)n * K : 0) + chunk * 8;
+        w_dst[p] = PM * 128 + swizzled(r, chunk);
+    }
+    const int steps = K / PK;
+    auto fill = [&](int step) {
+        const uint32_t stage = base + (uint32_t)(step % PSTAGES) * (PM + PN) * 128;
+        const int k0 = step * PK;
+#pragma unroll
+        for (int p = 0; p < 2; ++p) cp_async16(stage + a_dst[p], a_src[p] + k0, a_bytes[p]);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) cp_async16(stage + w_dst[p], w_src[p] + k0, w_bytes[p]);
+    };
+    for (int s = 0; s < PSTAGES - 1; ++s) {
+        if (s < steps) fill(s);
+        cp_async_commit();
+    }
+    const int wm = warp >> 2, wn = warp & 3;          // the warp's 32 x 32 part of the tile
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0f;
+    for (int step = 0; step < steps; ++step) {
+        cp_async_wait<PSTAGES - 2>();
+        __syncthreads();                               // the stage is complete, and the stage filled next is free
+        if (step + PSTAGES - 1 < steps) fill(step + PSTAGES - 1);
+        cp_async_commit();
+        const uint32_t stage = base + (uint32_t)(step % PSTAGES) * (PM + PN) * 128;
+#pragma unroll
+        for (int ks = 0; ks < PK / 16; ++ks) {
+            uint32_t a[2][4], b[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                ldmatrix_x4(a[i], stage + swizzled(wm * 32 + i * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+#pragma unroll
+            for (int j = 0; j < 2; ++j)                // two n-tiles of eight features a load
+                ldmatrix_x4(b[j], stage + PM * 128 +
+                                      swizzled(wn * 32 + j * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_bf16_16816(acc[i][j], a[i], &b[j >> 1][(j & 1) * 2]);
+        }
+    }
+    cp_async_wait<0>();
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int a = rows_of[wm * 32 + i * 16 + g + half * 8];
+            if (a < 0) continue;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int n = n0 + wn * 32 + j * 8 + 2 * t + e;
+                    if (n >= N) continue;
+                    float v = acc[i][j][half * 2 + e];
+                    if (EPI == EXP_SQUARED_RELU) {
+                        v = fmaxf(v, 0.0f);
+                        v *= v;
+                    }
+                    Elem<O>::store(out + (int64_t)a * out_stride + n, v);
+                }
+        }
+}
+
 // ----------------------------------------------------------------------------- the weighted sum
 
 __global__ void expert_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
@@ -360,10 +458,31 @@ int launch_linear(const void* in, int64_t in_stride, const void* W, void* out, i
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 
+template <typename O, int EPI>
+int launch_linear_pipe(const void* in, int64_t in_stride, const void* W, void* out, int64_t out_stride,
+                       const int* offsets, const int* order, int assignments, int experts, int top_div, int N, int K,
+                       cudaStream_t stream) {
+    const dim3 grid((N + PN - 1) / PN, (assignments + PM - 1) / PM + experts);
+    if (grid.y > 65535) return TB_ERR_BAD_SIZE;
+    auto kernel = expert_linear_pipe_kernel<O, EPI>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPipeSmem);
+    if (err != cudaSuccess) return (int)err;
+    cudaError_t launched = tb_launch_pdl(kernel, grid, dim3(256), (size_t)kPipeSmem, stream, (const __nv_bfloat16*)in,
+                                         in_stride, (const __nv_bfloat16*)W, (O*)out, out_stride, offsets, order,
+                                         experts, top_div, N, K);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
 template <typename O>
 int launch_linear_mma(const void* in, int64_t in_stride, const void* W, void* out, int64_t out_stride,
                       const int* offsets, const int* order, int assignments, int experts, int top_div, int N, int K,
                       int epilogue, cudaStream_t stream) {
+    if (K % PK == 0)
+        return epilogue == EXP_SQUARED_RELU
+                   ? launch_linear_pipe<O, EXP_SQUARED_RELU>(in, in_stride, W, out, out_stride, offsets, order, assignments,
+                                                             experts, top_div, N, K, stream)
+                   : launch_linear_pipe<O, EXP_PLAIN>(in, in_stride, W, out, out_stride, offsets, order, assignments,
+                                                      experts, top_div, N, K, stream);
     const dim3 grid((N + BN - 1) / BN, (assignments + BM - 1) / BM + experts);
     if (grid.y > 65535) return TB_ERR_BAD_SIZE;
     cudaError_t launched;
@@ -379,33 +498,6 @@ int launch_linear_mma(const void* in, int64_t in_stride, const void* W, void* ou
 }
 
 }  // namespace
-
-// x: [rows, width] (row stride x_stride); router: 32-bit [experts, width]; ids: int32 [rows, top]; weights: 32-bit
-// [rows, top].
-TB_EXPORT int tb_route_topk(const void* x, int64_t x_stride, const float* router, int* ids, float* weights, int rows,
-                            int width, int experts, int top, int dtype, cudaStream_t stream) {
-    if (rows == 0) return 0;
-    if (width < 1 || experts < 1 || top < 1 || top > experts) return TB_ERR_BAD_SIZE;
-    const size_t smem = (size_t)kRouteWarps * (width + experts) * sizeof(float);
-    if (smem > 200 * 1024) return TB_ERR_BAD_SIZE;
-    const dim3 grid((rows + kRouteWarps - 1) / kRouteWarps);
-    cudaError_t launched;
-#define TB_ROUTE(T)                                                                                                 \
-    do {                                                                                                            \
-        auto kernel = route_topk_kernel<T>;                                                                         \
-        if (smem > 40 * 1024) {                                                                                     \
-            cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            if (err != cudaSuccess) return (int)err;                                                                \
-        }                                                                                                           \
-        launched = tb_launch_pdl(kernel, grid, dim3(kRouteWarps * 32), smem, stream, (const T*)x, x_stride, router, \
-                                 ids, weights, rows, width, experts, top);                                          \
-    } while (0)
-    if (dtype == TB_F32) TB_ROUTE(float);
-    else if (dtype == TB_BF16) TB_ROUTE(__nv_bfloat16);
-    else return TB_ERR_BAD_DTYPE;
-#undef TB_ROUTE
-    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
-}
 
 // logits: 32-bit [rows, experts], contiguous.
 TB_EXPORT int tb_choose_topk(const float* logits, int* ids, float* weights, int rows, int experts, int top,
@@ -430,8 +522,8 @@ TB_EXPORT int tb_expert_plan(const int* ids, int assignments, int experts, int* 
 
 // in: [*, K] of dtype (row stride in_stride); W: [experts, N, K] of dtype; out: [assignments, N] of out_dtype (row
 // stride out_stride); top_div: the source row of assignment a is a / top_div.  epilogue: 0 plain, 1 squared ReLU.
-// tensor_cores != 0 asks for the mma.sync kernel (bfloat16, K a multiple of 32, 16-byte aligned rows); the entry point
-// refuses it where it cannot run.
+// tensor_cores != 0 asks for the mma.sync kernels (bfloat16, K a multiple of 32, 16-byte aligned rows; the pipelined
+// one where K is a multiple of 64); the entry point refuses it where it cannot run.
 TB_EXPORT int tb_expert_linear(const void* in, int64_t in_stride, const void* W, void* out, int64_t out_stride,
                                const int* offsets, const int* order, int assignments, int experts, int top_div, int N,
                                int K, int epilogue, int dtype, int out_dtype, int tensor_cores, cudaStream_t stream) {

@@ -9,7 +9,6 @@
 //   tb_add_bias           y[t, j] += b[j]                      (y 32-bit or bfloat16, b 32-bit)
 //   tb_scale_rows         y[t, j] *= s                         (32-bit y)
 //   tb_add_rows           a[t, j] += b[t, j]                   (32-bit)
-//   tb_widen_rows         out[t, j] = float(x[t, j])             (bfloat16 rows as the operand of a 32-bit product)
 //   tb_embedding_scaled   out[t, :] = float(table[token[t], :]) * s   (32-bit out; the table 32-bit or bfloat16)
 #include "common.cuh"
 
@@ -101,16 +100,6 @@ __global__ void add_rows_kernel(float* __restrict__ a, const float* __restrict__
     pdl_wait();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
         a[i] += b[i];
-}
-
-__global__ void widen_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_stride, float* __restrict__ out,
-                                  int width) {
-    pdl_trigger();
-    pdl_wait();
-    const __nv_bfloat16* xr = x + (int64_t)blockIdx.x * x_stride;
-    float* o = out + (int64_t)blockIdx.x * width;
-    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < width; j += gridDim.y * blockDim.x)
-        o[j] = __bfloat162float(xr[j]);
 }
 
 template <typename T>
@@ -212,13 +201,6 @@ TB_EXPORT int tb_scale_rows(float* y, int64_t total, float s, cudaStream_t strea
 TB_EXPORT int tb_add_rows(float* a, const float* b, int64_t total, cudaStream_t stream) {
     if (total == 0) return 0;
     cudaError_t launched = tb_launch_pdl(add_rows_kernel, dim3(grid_for(total, 256)), dim3(256), 0, stream, a, b, total);
-    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
-}
-
-TB_EXPORT int tb_widen_rows(const void* x, int64_t x_stride, float* out, int rows, int width, cudaStream_t stream) {
-    if (rows == 0 || width == 0) return 0;
-    cudaError_t launched = tb_launch_pdl(widen_rows_kernel, row_grid(rows, width, 256), dim3(256), 0, stream,
-                                         (const __nv_bfloat16*)x, x_stride, out, width);
     return launched == cudaSuccess ? tb_launch_status() : (int)launched;
 }
 

@@ -1004,38 +1004,9 @@ def rope_norm_cache(proj: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor
 EXPERT_PLAIN, EXPERT_SQUARED_RELU = 0, 1
 
 
-def route_topk(x: torch.Tensor, router: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> None:
-    """Router logits ``x @ router^T`` in 32-bit (``router`` float32 ``[E, W]``), the ``top`` largest per row (largest
-    first) into ``ids`` (int32 ``[T, top]``) and the softmax over those into ``weights`` (float32 ``[T, top]``)."""
-    _cuda(x, router, ids, weights)
-    rows, width = x.shape
-    top = ids.shape[1]
-    _need(x.stride(1) == 1, "route_topk x")
-    _need(router.dtype == torch.float32 and router.is_contiguous() and router.shape[1] == width, "route_topk router")
-    _need(ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (rows, top), "route_topk ids")
-    _need(weights.dtype == torch.float32 and weights.is_contiguous() and weights.shape == (rows, top), "route_topk weights")
-    lib = load_library("experts")
-    _check(lib.tb_route_topk(_ptr(x), _i64(x.stride(0)), _ptr(router), _ptr(ids), _ptr(weights), _i32(rows), _i32(width),
-                             _i32(router.shape[0]), _i32(top), _i32(_code(x.dtype)), _stream()), "route_topk")
-
-
-ROUTE_FUSED_MAX_ROWS = 256     # up to here the router's product and the choice are one kernel, a warp a row
-
-
-def widen_rows(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """``out = float32(x)`` for bfloat16 rows ``x`` (row stride free) and a contiguous float32 ``out``."""
-    _cuda(x, out)
-    _need(x.dtype == torch.bfloat16 and x.stride(1) == 1 and out.dtype == torch.float32 and out.is_contiguous()
-          and out.shape == x.shape, "widen_rows x/out")
-    lib = load_library("pointwise")
-    _check(lib.tb_widen_rows(_ptr(x), _i64(x.stride(0)), _ptr(out), _i32(x.shape[0]), _i32(x.shape[1]), _stream()),
-           "widen_rows")
-    return out
-
-
 def choose_topk(logits: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> None:
     """The ``top`` largest of every row of ``logits`` (float32 ``[T, E]``; largest first) into ``ids`` and the softmax
-    over those into ``weights``: :func:`route_topk` without the router's product."""
+    over those alone into ``weights`` (the lowest index wins among equal logits)."""
     _cuda(logits, ids, weights)
     rows, experts = logits.shape
     top = ids.shape[1]

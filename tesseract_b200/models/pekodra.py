@@ -93,7 +93,7 @@ def pekodra_kernel_libraries(cfg: PekodraConfig, dtype: str):
     """The kernel files a Pekodra model of this run dtype calls: a first call compiles these and no others."""
     shared = ["elementwise", "parallel_norm", "pointwise", "rope_norm_cache", "attention_masked", "sampling"]
     if any(isinstance(layer.mlp, PekodraExperts) for layer in cfg.layers):
-        shared += ["experts"] + (["gemm_f32"] if dtype != "float32" else [])      # (the router's product is 32-bit)
+        shared.append("experts")
     if any(layer.mlp is None for layer in cfg.layers):
         shared.append("norm")          # a single pending update goes through the grouped norm's own kernel
     return shared + (["gemm_f32"] if dtype == "float32" else ["decode_linear", "skinny_tcgen05"])

@@ -2,8 +2,8 @@
 
 Per row ``h`` (the feed-forward's input):
 
-* router logits ``z = W_r h`` in 32-bit; the ``top_k`` largest are chosen (largest first) and weighted by the
-  softmax over the chosen logits alone;
+* router logits ``z = W_r h`` accumulated and kept in 32-bit; the ``top_k`` largest are chosen (largest first, the
+  lowest index of equal logits) and weighted by the softmax over the chosen logits alone;
 * an expert is ``down_e(act(up_e h))`` without biases, ``act`` the squared ReLU ``max(z, 0)^2``;
 * the output is the weighted sum of the chosen experts' outputs, slots in order, plus, if the model has one, a
   shared expert of the same form (and a size of its own) that every row takes.
@@ -46,7 +46,9 @@ class RoutedExperts(FeedForward):
         self.stream_f32 = p.get("stream") == "float32"
         if not 1 <= self.top_k <= self.num_experts:
             raise ValueError(f"top_k must lie between 1 and the {self.num_experts} experts, got {self.top_k}")
-        self.router = runtime.vector_f32(tensors["router"])                    # the router's product is 32-bit
+        # the router's product: the run dtype's operands (a bfloat16 weight and row multiply exactly in 32-bit),
+        # 32-bit accumulation, 32-bit logits; in a float32 run the package's own 32-bit product
+        self.router = Linear(tensors["router"], runtime)
         experts = range(self.num_experts)
         self.up = torch.stack([tensors[f"up.{e}"] for e in experts]).to(device=runtime.device, dtype=runtime.dtype).contiguous()
         self.down = torch.stack([tensors[f"down.{e}"] for e in experts]).to(device=runtime.device, dtype=runtime.dtype).contiguous()
@@ -76,24 +78,18 @@ class RoutedExperts(FeedForward):
 
     def products(self):
         """``(name, Linear, epilogue)`` of the products that go through the kernel plan (the shared expert's)."""
-        if not self.shared_size:
-            return []
-        return [("shared up", self.shared_up, plan.BF16),
-                ("shared down", self.shared_down, plan.F32 if self.stream_f32 else plan.BF16)]
+        out = [("router", self.router, plan.F32)]
+        if self.shared_size:
+            out += [("shared up", self.shared_up, plan.BF16),
+                    ("shared down", self.shared_down, plan.F32 if self.stream_f32 else plan.BF16)]
+        return out
 
     def route(self, x: torch.Tensor):
         """``(ids int32 [rows, top_k], weights float32 [rows, top_k])`` of the rows of ``x``."""
         rows = x.shape[0]
         ids = torch.empty((rows, self.top_k), dtype=torch.int32, device=x.device)
         weights = torch.empty((rows, self.top_k), dtype=torch.float32, device=x.device)
-        if rows <= kernels.ROUTE_FUSED_MAX_ROWS:
-            kernels.route_topk(x, self.router, ids, weights)
-            return ids, weights
-        # many rows: the logits through the package's 32-bit product (operands widened exactly), then the choice
-        wide = x if x.dtype == torch.float32 else kernels.widen_rows(x, torch.empty(x.shape, dtype=torch.float32, device=x.device))
-        logits = torch.empty((rows, self.num_experts), dtype=torch.float32, device=x.device)
-        kernels.gemm_f32_nt(wide.contiguous() if not wide.is_contiguous() else wide, self.router, logits)
-        kernels.choose_topk(logits, ids, weights)
+        kernels.choose_topk(self.router.forward(x, float32_out=True), ids, weights)
         return ids, weights
 
     def forward(self, x, ctx: StepContext, follow=None):

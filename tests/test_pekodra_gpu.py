@@ -289,27 +289,34 @@ def test_window_attention_sees_exactly_its_keys(dtype, heads, kv_heads, d, dv, w
 
 
 @pytest.mark.parametrize("rows", [1, 7, 300])
-@pytest.mark.parametrize("experts,top,width", [(5, 2, 40), (33, 4, 64), (16, 1, 200), (3, 3, 24), (64, 6, 1024)])
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_router_chooses_the_largest_and_weighs_the_chosen_alone(rows, experts, top, width, dtype):
+@pytest.mark.parametrize("experts,top", [(5, 2), (33, 4), (16, 1), (3, 3), (64, 6), (200, 8)])
+def test_the_choice_takes_the_largest_and_weighs_the_chosen_alone(rows, experts, top):
     from tesseract_b200 import kernels
 
     g = torch.Generator().manual_seed(experts + rows)
-    x = torch.randn(rows, width, generator=g).to(dtype)
-    router = (torch.randn(experts, width, generator=g) * 2.0 * width ** -0.5).to(torch.bfloat16).float()
-    want_ids, want_weights = plain.route(x.double(), router.double(), top)
+    logits = torch.randn(rows, experts, generator=g) * 3.0
+    logits[0, experts - 1] = logits[0, 0] = 50.0                   # equal logits: the lower index goes first
+    values, want_ids = torch.topk(logits.double(), top, dim=-1)
     ids = torch.empty(rows, top, dtype=torch.int32, device=dev())
     weights = torch.empty(rows, top, dtype=torch.float32, device=dev())
-    kernels.route_topk(x.to(dev()), router.to(dev()), ids, weights)
+    kernels.choose_topk(logits.to(dev()), ids, weights)
+    assert ids[0, 0].item() == 0 and (top == 1 or ids[0, 1].item() == experts - 1)
+    assert torch.equal(torch.sort(ids.cpu().long(), dim=1).values[1:], torch.sort(want_ids, dim=1).values[1:])
+    chosen = torch.gather(logits.double(), 1, ids.cpu().long())
+    assert torch.all(chosen[:, :-1] >= chosen[:, 1:]), "largest first"
+    assert torch.allclose(weights.cpu().double(), torch.softmax(chosen, dim=-1), rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows", [1, 20, 300])
+def test_router_of_the_part_against_plain(dtype, rows):
+    part, weights, mlp = _experts_part(dtype, 64, 12, 3, 16, None, seed=rows)
+    g = torch.Generator().manual_seed(rows + 1)
+    x = torch.randn(rows, 64, generator=g).to(dtype)
+    want_ids, want_weights = plain.route(x.double(), weights["router"], 3)
+    ids, got = part.route(x.to(dev()))
     assert torch.equal(ids.cpu().long(), want_ids)
-    assert torch.allclose(weights.cpu().double(), want_weights, rtol=1e-5, atol=1e-6)
-    assert torch.allclose(weights.sum(dim=1).cpu(), torch.ones(rows), atol=1e-6)
-    # the choice alone, from logits of the 32-bit product
-    logits = torch.empty(rows, experts, dtype=torch.float32, device=dev())
-    kernels.gemm_f32_nt(x.float().to(dev()), router.to(dev()), logits)
-    kernels.choose_topk(logits, ids, weights)
-    assert torch.equal(ids.cpu().long(), want_ids)
-    assert torch.allclose(weights.cpu().double(), want_weights, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(got.cpu().double(), want_weights, rtol=1e-4, atol=1e-6)
 
 
 def _experts_part(dtype, width, experts, top, size, shared, seed):
@@ -339,7 +346,7 @@ def _experts_part(dtype, width, experts, top, size, shared, seed):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("width,experts,top,size,shared", [(64, 3, 2, 32, 48), (40, 5, 1, 24, None), (96, 16, 3, 64, 128),
-                                                           (32, 4, 4, 8, 16), (66, 7, 2, 20, 10)])
+                                                           (32, 4, 4, 8, 16), (66, 7, 2, 20, 10), (256, 6, 2, 320, 64)])
 @pytest.mark.parametrize("rows", [1, 9, 300])
 def test_routed_experts_alone(dtype, width, experts, top, size, shared, rows):
     """Router, grouping, both grouped products and the weighted sum against the plain mixture: single rows, a few,
