@@ -58,6 +58,7 @@ SOURCES: Dict[str, List[str]] = {
     "pointwise": [],
     "rope_norm_cache": [],
     "experts": [],
+    "attention_prompt_mma": [],
 }
 
 

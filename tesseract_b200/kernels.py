@@ -834,6 +834,34 @@ def attention_masked(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
     return out
 
 
+def attention_prompt_mma_supported(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+    """Whether the tensor-core prompt attention takes these head sizes (bfloat16 only)."""
+    return dtype == torch.bfloat16 and bool(load_library("attention_prompt_mma").tb_attention_prompt_mma_supported(
+        _i32(dim), _i32(vdim)))
+
+
+def attention_prompt_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
+                         row_start: torch.Tensor, block_table: torch.Tensor, *, num_seqs: int, heads: int,
+                         kv_heads: int, dim: int, vdim: int, page_size: int, mask_kind: int, mask_size: int,
+                         scale: float) -> torch.Tensor:
+    """:func:`attention_masked` (no sink, no gate) for bfloat16 prompt portions on the tensor cores: scores from
+    exact bfloat16 products with 32-bit accumulation, 32-bit softmax, the 32-bit weights split in two bfloat16 halves
+    for the product with the values.  The rows of a sequence (``row_start``) stand at consecutive positions."""
+    _cuda(q, out, cache, positions, row_start, block_table)
+    rows = q.shape[0]
+    _need(q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape[1] == heads * dim, "attention_prompt_mma q")
+    _need(out.stride(1) == 1 and out.shape == (rows, heads * vdim) and out.dtype == q.dtype, "attention_prompt_mma out")
+    _need(cache.dtype == q.dtype and cache.is_contiguous(), "attention_prompt_mma cache")
+    _need(row_start.dtype == torch.int32 and row_start.numel() >= num_seqs + 1, "attention_prompt_mma row_start")
+    lib = load_library("attention_prompt_mma")
+    _check(lib.tb_attention_prompt_mma(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
+                                       _ptr(positions), _ptr(row_start), _ptr(block_table), _i32(block_table.stride(0)),
+                                       _i32(rows), _i32(num_seqs), _i32(heads), _i32(kv_heads), _i32(dim), _i32(vdim),
+                                       _i32(page_size), _i32(mask_kind), _i32(mask_size), _f32(scale), _stream()),
+           "attention_prompt_mma")
+    return out
+
+
 def gated_recurrence(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor,
                      out: torch.Tensor, row_start: torch.Tensor, state_slots: torch.Tensor, *, num_seqs: int,
                      max_new: int) -> torch.Tensor:

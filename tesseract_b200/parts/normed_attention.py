@@ -13,7 +13,8 @@ Per row ``h`` (the mixer's input):
 * the output projection's result comes out in 32-bit for a residual stream kept in 32-bit (``stream`` = ``"float32"``).
 
 Rotation, normalisation and the cache write are one kernel; the attention kernel is the one the other mixers with
-keys and values of separate widths use.
+keys and values of separate widths use, or, for bfloat16 steps of many rows and head sizes it is built for, the
+tensor-core kernel with the same masks and 32-bit scores and weights (the kernel plan decides).
 """
 
 from __future__ import annotations
@@ -22,7 +23,7 @@ from typing import Dict, Mapping
 
 import torch
 
-from .. import kernels
+from .. import kernels, plan
 from ..config.spec import PartSpec
 from ..weights.loader import ExpectedTensor
 from .base import MIXERS, POSITION_ENCODINGS, DeferredNorm, Mixer, PagedKeyValueNeed, Runtime, StepContext
@@ -119,8 +120,14 @@ class NormedAttention(Mixer):
                                 dim=self.key_dim, vdim=self.value_dim, rot_dims=self.rot_dims,
                                 unit_norm=self.unit_norm, eps=self.qk_norm_eps, page_size=cache.page_size)
         attended = torch.empty((rows, self.o_width), dtype=proj.dtype, device=proj.device)
-        kernels.attention_masked(q, None, attended, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
-                                 heads=self.num_heads, kv_heads=self.num_kv_heads, dim=self.key_dim,
-                                 vdim=self.value_dim, page_size=cache.page_size, mask_kind=_MASKS[self.mask_kind],
-                                 mask_size=self.mask_size, sink=False, scale=self.scale)
+        if plan.masked_attention(proj.dtype, rows, self.key_dim, self.value_dim) == "attention_prompt_mma":
+            kernels.attention_prompt_mma(q, attended, cache.storage, ctx.positions, ctx.row_start, group.block_table,
+                                         num_seqs=ctx.num_seqs, heads=self.num_heads, kv_heads=self.num_kv_heads,
+                                         dim=self.key_dim, vdim=self.value_dim, page_size=cache.page_size,
+                                         mask_kind=_MASKS[self.mask_kind], mask_size=self.mask_size, scale=self.scale)
+        else:
+            kernels.attention_masked(q, None, attended, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
+                                     heads=self.num_heads, kv_heads=self.num_kv_heads, dim=self.key_dim,
+                                     vdim=self.value_dim, page_size=cache.page_size, mask_kind=_MASKS[self.mask_kind],
+                                     mask_size=self.mask_size, sink=False, scale=self.scale)
         return self.o_proj.forward(attended, float32_out=self.stream_f32)

@@ -136,6 +136,26 @@ def product(dtype: torch.dtype, rows: int, out_features: int, in_features: int, 
     return ProductPlan("library", False, epilogue)
 
 
+MASKED_PROMPT_MIN_ROWS = 257      # from here on a step's masked attention may go to the tensor cores
+
+
+@lru_cache(maxsize=None)
+def _prompt_mma_takes(dtype: torch.dtype, key_dim: int, value_dim: int) -> bool:
+    return kernels.attention_prompt_mma_supported(dtype, key_dim, value_dim)
+
+
+def masked_attention(dtype: torch.dtype, rows: int, key_dim: int, value_dim: int, sink: bool = False,
+                     gated: bool = False) -> str:
+    """The kernel for attention with 32-bit scores and weights over keys and values of separate widths:
+    ``"attention_prompt_mma"`` (tensor cores; bfloat16, no sink, no gate, head sizes it is built for) for steps of
+    more than 256 rows, where ``attention_masked`` stops sharing a row's keys between warps: 2,048 rows of 32 heads
+    of 64 under a window of 512 take 555 us there.  ``"attention_masked"`` otherwise."""
+    if (rows >= MASKED_PROMPT_MIN_ROWS and not sink and not gated and dtype == torch.bfloat16
+            and _prompt_mma_takes(dtype, key_dim, value_dim)):
+        return "attention_prompt_mma"
+    return "attention_masked"
+
+
 def attention_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 64,
                      sms: Optional[int] = None) -> int:
     """How many key splits the decode kernel uses.

@@ -55,6 +55,11 @@ TINY_PEKODRA = {
           "logit_scale": 0.25, "loop": {"start": 1, "stop": 2, "times": 1},
           "layers": [layer(attention(2, 2, 8, 8, 1, (8, 20.0, None), 0.4), dense(16)),
                      layer(attention(4, 1, 16, 8, 17, (12, 500.0, (16.0, 8, 1.0, 0.25)), 0.2), moe(9, 4, 8, 16))]},
+    # head sizes and prompt lengths that send prompt portions to the tensor-core attention: a window, and all keys
+    "e": {"architecture": "Pekodra", "width": 64, "vocab": 90, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.5},
+          "logit_scale": 0.5, "loop": {"start": 0, "stop": 1, "times": 2},
+          "layers": [layer(attention(2, 1, 64, 64, 100, (32, 10000.0, (4.0, 128, 16.0, 1.0)), 0.125), dense(48)),
+                     layer(attention(4, 2, 64, 48, None, (64, 100.0, None), 0.2), moe(4, 2, 16, 32))]},
 }
 
 

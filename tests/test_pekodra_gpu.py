@@ -223,7 +223,8 @@ def _step_context(positions, page_order, page):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv_heads,d,dv", [(4, 2, 16, 24), (6, 2, 64, 48), (3, 1, 20, 12)])
+@pytest.mark.parametrize("heads,kv_heads,d,dv", [(4, 2, 16, 24), (6, 2, 64, 48), (3, 1, 20, 12), (4, 1, 64, 64),
+                                                 (2, 2, 128, 128), (2, 1, 64, 128), (2, 1, 128, 64)])
 @pytest.mark.parametrize("window", [33, 16, 5, 1, None])
 def test_window_attention_sees_exactly_its_keys(dtype, heads, kv_heads, d, dv, window):
     """A row whose query equals one key's direction returns that key's value if the window lets the row see the key,
@@ -319,6 +320,63 @@ def test_router_of_the_part_against_plain(dtype, rows):
     assert torch.allclose(got.cpu().double(), want_weights, rtol=1e-4, atol=1e-6)
 
 
+@pytest.mark.parametrize("d,dv", [(64, 64), (64, 48), (128, 128), (64, 128), (128, 64)])
+@pytest.mark.parametrize("kind,size", [("window", 100), ("window", 7), ("causal", 0), ("blocks", 90), ("blocks", 16)])
+def test_tensor_core_prompt_attention_against_plain_and_the_row_kernel(d, dv, kind, size):
+    """Three sequences in one step: a whole prompt of 300 rows, 70 rows that continue a sequence at position 500 (the
+    keys before them were stored by earlier steps), and a single row at position 40; pages in scrambled order."""
+    from tesseract_b200 import kernels
+
+    heads, kv_heads, page = 4, 2, 16
+    scale = 4.0 / d ** 0.5                                           # sharp softmaxes: the weights matter
+    spans = [(0, 300), (500, 70), (40, 1)]                           # (first position, rows) of each sequence's portion
+    g = torch.Generator().manual_seed(d + dv + size)
+    lengths = [begin + n for begin, n in spans]
+    pages_each = [-(-length // page) for length in lengths]
+    order = torch.randperm(sum(pages_each), generator=g).tolist()
+    table = torch.zeros(3, max(pages_each), dtype=torch.int32)
+    storage = torch.full((sum(pages_each) + 1, kv_heads * page * (d + dv)), 7.0, dtype=torch.bfloat16)
+    qs, wants, used = [], [], 0
+    mask_of = {"window": lambda T: plain.window_mask(T, size), "causal": lambda T: plain.window_mask(T, None),
+               "blocks": lambda T: plain.window_mask(T, None) & ((torch.arange(T)[:, None] // size) == (torch.arange(T)[None, :] // size))}
+    for s, (begin, n) in enumerate(spans):
+        T = lengths[s]
+        k = torch.randn(T, kv_heads, d, generator=g).to(torch.bfloat16)
+        v = torch.randn(T, kv_heads, dv, generator=g).to(torch.bfloat16)
+        q = torch.randn(T, heads, d, generator=g).to(torch.bfloat16)
+        mine = [1 + p for p in order[used:used + pages_each[s]]]
+        used += pages_each[s]
+        laid, _ = _pages_from(k, v, page, mine)
+        for page_id in mine:
+            storage[page_id] = laid[page_id]
+        table[s, :len(mine)] = torch.tensor(mine, dtype=torch.int32)
+        seen = mask_of[kind](T)
+        out = torch.zeros(T, heads, dv, dtype=torch.float64)
+        for h in range(heads):
+            scores = (q[:, h].double() @ k[:, h // (heads // kv_heads)].double().T) * scale
+            out[:, h] = torch.softmax(scores.masked_fill(~seen, float("-inf")), dim=-1) @ v[:, h // (heads // kv_heads)].double()
+        qs.append(q[begin:].reshape(n, heads * d))
+        wants.append(out[begin:].reshape(n, heads * dv))
+    q_all, want = torch.cat(qs).to(dev()), torch.cat(wants)
+    rows = q_all.shape[0]
+    positions = torch.cat([torch.arange(b, b + n) for b, n in spans]).to(torch.int32).to(dev())
+    seq_of_row = torch.cat([torch.full((n,), s) for s, (_, n) in enumerate(spans)]).to(torch.int32).to(dev())
+    row_start = torch.tensor([0, 300, 370, 371], dtype=torch.int32, device=dev())
+    mask_kind = {"causal": kernels.MASK_CAUSAL, "window": kernels.MASK_WINDOW, "blocks": kernels.MASK_BLOCKS}[kind]
+    got = torch.empty(rows, heads * dv, dtype=torch.bfloat16, device=dev())
+    kernels.attention_prompt_mma(q_all, got, storage.to(dev()), positions, row_start, table.to(dev()), num_seqs=3,
+                                 heads=heads, kv_heads=kv_heads, dim=d, vdim=dv, page_size=page, mask_kind=mask_kind,
+                                 mask_size=size, scale=scale)
+    other = torch.empty_like(got)
+    kernels.attention_masked(q_all, None, other, storage.to(dev()), positions, seq_of_row, table.to(dev()), heads=heads,
+                             kv_heads=kv_heads, dim=d, vdim=dv, page_size=page, mask_kind=mask_kind, mask_size=size,
+                             sink=False, scale=scale)
+    assert (got.cpu().double() - want).abs().max().item() <= 2e-2          # the output's own rounding to bfloat16
+    assert (got.float() - other.float()).abs().max().item() <= 2e-2
+    # the weights are 32-bit: an output far below the largest one keeps its relative accuracy
+    assert ((got.cpu().double() - want).abs() <= 1e-2 * want.abs() + 1e-3).all()
+
+
 def _experts_part(dtype, width, experts, top, size, shared, seed):
     from tesseract_b200.config.spec import PartSpec
     from tesseract_b200.parts import FEED_FORWARDS
@@ -405,7 +463,7 @@ def test_gated_feed_forward_and_origin_mix_alone(dtype):
 # ----------------------------------------------------------------------------- whole models
 
 
-LENGTHS = {"a": [1, 2, 3, 14, 40, 97], "b": [5, 33, 66, 130], "c": [4, 27, 81], "d": [1, 9, 70]}
+LENGTHS = {"a": [1, 2, 3, 14, 40, 97], "b": [5, 33, 66, 130], "c": [4, 27, 81], "d": [1, 9, 70], "e": [300, 5, 270]}
 
 
 def make_requests(name):
@@ -553,7 +611,7 @@ def test_every_layer_run_matches_plain(engines, folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "portions", "twos"])
 def test_cuts_match_plain(engines, folders, name, dtype, cut):
     """Whole prompts, prompts with a decoded tail (over which the windows move), portions of changing size, and
