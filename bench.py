@@ -980,7 +980,7 @@ def pekodra_kernels(size, pk):
                 line["frac_of_measured_bf16"] = round(flops / us / 1e6 / pk["bf16_tflops"], 4)
         out[name] = line
 
-    for label, rows, seqs, begin in (("prefill_2048", 2048, 1, 0), ("decode_64", 64, 64, 2047)):
+    for label, rows, seqs, begin in (("prefill_2048", 2048, 1, 0), ("decode_64", 64, 64, 2047), ("decode_8", 8, 8, 2047)):
         new = rows // seqs
         positions = (torch.arange(rows, dtype=torch.int32, device=dev) % new) + begin
         seq_of_row = torch.arange(rows, dtype=torch.int32, device=dev) // new
@@ -1026,6 +1026,21 @@ def pekodra_kernels(size, pk):
         kv_read = (2048 if new > 1 else seqs * min(begin + 1, window)) * G * 2 * d * 2
         timed(f"attention_masked (window {window})/{label}", attend, rows * H * d * 2 * 2 + kv_read,
               flops=keys_seen * H * 2 * d * 2)
+
+        if new > 1:
+            row_start = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * new
+
+            def attend_mma(k):
+                q = torch.randn(rows, H * d, device=dev).bfloat16()
+                o = torch.empty(rows, H * d, dtype=torch.bfloat16, device=dev)
+                cache = torch.randn(seqs * pages_per_seq + 1, page_elems, device=dev).bfloat16()
+                return lambda: kernels.attention_prompt_mma(q, o, cache, positions, row_start, table, num_seqs=seqs,
+                                                            heads=H, kv_heads=G, dim=d, vdim=d, page_size=page,
+                                                            mask_kind=kernels.MASK_WINDOW, mask_size=window,
+                                                            scale=d ** -0.5)
+
+            timed(f"attention_prompt_mma (window {window})/{label}", attend_mma, rows * H * d * 2 * 2 + kv_read,
+                  flops=keys_seen * H * 2 * d * 2, tensor=True)
 
         def act(k):
             gu = torch.randn(rows, 2 * F, device=dev).bfloat16()

@@ -23,7 +23,7 @@
 // but a few of the same keys and meet in L1.  Scores: a lane a key, the key's packets against the queries in
 // shared memory (read four numbers at a time).  Values: the warp is cut into groups of lanes that share a value
 // row, a lane a packet of columns, the weights passed through shared memory; the groups' partial sums meet at the
-// end in a fixed butterfly.  In a step of few rows (decoded ones) a block is one row instead, and its four warps
+// end in a fixed butterfly.  In a step of few rows (decoded ones) a block is one row instead, and its four or eight warps
 // share the row's keys; which of the two runs depends on the number of rows of the step, so a row's values are the
 // same in every batch up to the order of a few sums.  The element kernel takes every other size, a number at a time.
 #include "common.cuh"
@@ -130,12 +130,16 @@ attention_masked_kernel(const T* __restrict__ q, int64_t q_stride, const T* __re
 
 constexpr int kRowsPerBlock = 8;      // warps of a block: neighbouring rows of the same heads
 constexpr int kSplitWarps = 4;        // warps of a block that share one row's keys (steps of few rows)
+constexpr int kSplitWarpsLong = 8;    // the same where few rows each see many keys (2.55 -> 1.49 ms a decode step of
+                                      // eight rows under windows of 512; at 64 rows, or with at most 256 keys a row,
+                                      // eight warps lose 3 to 9 %)
+constexpr int kLongSpan = 256, kLongMaxRows = 32;
 
 // HPW: query heads of one kv head that a warp takes together (1 to 4, a divisor of the heads per kv head); NP: packets of value columns per lane;
 // lv: lanes that share a value row in the value phase (a power of two).
-// SPLIT: a block is ONE row (a step of few rows, decoded ones for instance): its four warps take every fourth
-// block of 32 keys each and their partial results (running maximum, sum, accumulator) meet in shared memory.
-template <typename T, int HPW, int NP, bool SPLIT>
+// SPLITW > 0: a block is ONE row (a step of few rows, decoded ones for instance): its SPLITW warps take every
+// SPLITW-th block of 32 keys each and their partial results (running maximum, sum, accumulator) meet in shared memory.
+template <typename T, int HPW, int NP, int SPLITW>
 __global__ void __launch_bounds__(kRowsPerBlock * 32, 3)
 attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict__ gate,
                                 int64_t gate_stride, T* __restrict__ out, int64_t out_stride,
@@ -144,7 +148,8 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
                                 int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind,
                                 int mask_size, int sink, float scale, int lv) {
     constexpr int N = Packet<T>::N;
-    constexpr int WARPS = SPLIT ? kSplitWarps : kRowsPerBlock;
+    constexpr bool SPLIT = SPLITW > 0;
+    constexpr int WARPS = SPLIT ? SPLITW : kRowsPerBlock;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_trigger();
     pdl_wait();                                       // queries, pages and the step's metadata come from kernels in front
@@ -340,7 +345,7 @@ attention_masked_packets_kernel(const T* __restrict__ q, int64_t q_stride, const
 
 constexpr int kSplitMaxRows = 256;     // steps of at most this many rows give every row a block of its own
 
-template <typename T, int HPW, int NP, bool SPLIT>
+template <typename T, int HPW, int NP, int SPLITW>
 int launch_packets_as(const void* q, int64_t q_stride, const void* gate, int64_t gate_stride, void* out,
                       int64_t out_stride, const void* cache, const int* positions, const int* seq_of_row,
                       const int* block_table, int bt_stride, int rows, int heads, int kv_heads, int dim, int vdim,
@@ -348,11 +353,12 @@ int launch_packets_as(const void* q, int64_t q_stride, const void* gate, int64_t
     constexpr int N = Packet<T>::N;
     int lv = 1;
     while (lv < 32 && lv * NP < vdim / N) lv <<= 1;
-    constexpr int WARPS = SPLIT ? kSplitWarps : kRowsPerBlock;
+    constexpr bool SPLIT = SPLITW > 0;
+    constexpr int WARPS = SPLIT ? SPLITW : kRowsPerBlock;
     const dim3 grid(SPLIT ? rows : (rows + WARPS - 1) / WARPS, heads / HPW);
     const size_t smem = WARPS * (32 * sizeof(int64_t) + (size_t)HPW * (32 + dim) * sizeof(float)) +
                         (SPLIT ? (size_t)WARPS * HPW * (vdim + 2) * sizeof(float) : 0);
-    auto kernel = attention_masked_packets_kernel<T, HPW, NP, SPLIT>;
+    auto kernel = attention_masked_packets_kernel<T, HPW, NP, SPLITW>;
     if (smem > 40 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
@@ -371,22 +377,22 @@ int launch_packets(const void* q, int64_t q_stride, const void* gate, int64_t ga
                    int mask_size, int sink, float scale, cudaStream_t stream) {
     const int per = heads / kv_heads;
     const bool two = vdim / Packet<T>::N > 32;        // more value packets than lanes: two a lane
+    // (which form runs depends on the step's row count and the mask alone)
+    const bool long_span = rows <= kLongMaxRows && (mask_kind == MASK_CAUSAL || mask_size > kLongSpan);
+#define TB_PACKETS_AS(HPW, NP, SPLITW)                                                                               \
+    launch_packets_as<T, HPW, NP, SPLITW>(q, q_stride, gate, gate_stride, out, out_stride, cache, positions,         \
+                                          seq_of_row, block_table, bt_stride, rows, heads, kv_heads, dim, vdim,      \
+                                          page_size, mask_kind, mask_size, sink, scale, stream)
 #define TB_PACKETS(HPW, NP)                                                                                          \
-    return rows <= kSplitMaxRows                                                                                     \
-               ? launch_packets_as<T, HPW, NP, true>(q, q_stride, gate, gate_stride, out, out_stride, cache,         \
-                                                     positions, seq_of_row, block_table, bt_stride, rows, heads,     \
-                                                     kv_heads, dim, vdim, page_size, mask_kind, mask_size, sink,     \
-                                                     scale, stream)                                                  \
-               : launch_packets_as<T, HPW, NP, false>(q, q_stride, gate, gate_stride, out, out_stride, cache,        \
-                                                      positions, seq_of_row, block_table, bt_stride, rows, heads,    \
-                                                      kv_heads, dim, vdim, page_size, mask_kind, mask_size, sink,    \
-                                                      scale, stream)
+    return rows > kSplitMaxRows ? TB_PACKETS_AS(HPW, NP, 0)                                                          \
+                                : (long_span ? TB_PACKETS_AS(HPW, NP, kSplitWarpsLong) : TB_PACKETS_AS(HPW, NP, kSplitWarps))
     if (per % 4 == 0 && !two) TB_PACKETS(4, 1);
     if (per % 3 == 0 && !two) TB_PACKETS(3, 1);
     if (per % 2 == 0) { if (two) TB_PACKETS(2, 2); else TB_PACKETS(2, 1); }
     if (two) TB_PACKETS(1, 2);
     TB_PACKETS(1, 1);
 #undef TB_PACKETS
+#undef TB_PACKETS_AS
 }
 
 template <typename T, bool VEC>
