@@ -1042,6 +1042,18 @@ def pekodra_kernels(size, pk):
             timed(f"attention_prompt_mma (window {window})/{label}", attend_mma, rows * H * d * 2 * 2 + kv_read,
                   flops=keys_seen * H * 2 * d * 2, tensor=True)
 
+        if new == 1:
+            def attend_rows(k):
+                q = torch.randn(rows, H * d, device=dev).bfloat16()
+                o = torch.empty(rows, H * d, dtype=torch.bfloat16, device=dev)
+                cache = torch.randn(seqs * pages_per_seq + 1, page_elems, device=dev).bfloat16()
+                return lambda: kernels.attention_rows_mma(q, o, cache, positions, seq_of_row, table, heads=H, kv_heads=G,
+                                                          dim=d, vdim=d, page_size=page, mask_kind=kernels.MASK_WINDOW,
+                                                          mask_size=window, scale=d ** -0.5)
+
+            timed(f"attention_rows_mma (window {window})/{label}", attend_rows, rows * H * d * 2 * 2 + kv_read,
+                  flops=keys_seen * H * 2 * d * 2)
+
         def act(k):
             gu = torch.randn(rows, 2 * F, device=dev).bfloat16()
             bias = torch.randn(2 * F, device=dev)

@@ -1,5 +1,5 @@
-// Paged attention for prompt portions on the tensor cores, with 32-bit scores and weights kept to 32-bit accuracy:
-// the masks and page layout of attention_masked.cu (keys and values of separate widths; causal, sliding window or
+// Paged attention on the tensor cores, for prompt portions and (second kernel) for steps of few rows, with 32-bit
+// scores and weights kept to 32-bit accuracy: the masks and page layout of attention_masked.cu (keys and values of separate widths; causal, sliding window or
 // blocks of positions), for bfloat16 queries, keys and values.
 //
 //   S = Q K^T      mma.sync m16n8k16 on bfloat16 operands with 32-bit accumulators: the products of two bfloat16
@@ -254,6 +254,201 @@ attention_prompt_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __re
     }
 }
 
+// Steps of few rows (decoded ones): a block is ONE row and one kv head.  The query heads of that kv head (at most 16)
+// are the 16 rows of the first operand, so a key or value is fetched once for all of them; the block's four warps
+// share every tile of 64 keys, 16 keys a warp, each with a streaming softmax of its own, and their partial results
+// (maximum, sum, accumulator) meet in shared memory in warp order.
+template <int D, int DV>
+__global__ void __launch_bounds__(128)
+attention_rows_kernel(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__ out, int64_t out_stride,
+                      const bf16* __restrict__ cache, const int* __restrict__ positions,
+                      const int* __restrict__ seq_of_row, const int* __restrict__ block_table, int bt_stride, int heads,
+                      int kv_heads, int page_size, int mask_kind, int mask_size, float scale) {
+    constexpr int KS = D * 2 + 16, VS = DV * 2 + 16;
+    constexpr int STAGE = KT * (KS + VS);
+    constexpr int PART = DV + 2;                                  // a row's accumulator, maximum and sum
+    extern __shared__ __align__(128) unsigned char tile_smem[];   // two stages, then [4 warps][16 rows][PART] floats
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int row = blockIdx.x, kv_head = blockIdx.y, per = heads / kv_heads;
+    const int pos = positions[row], seq = seq_of_row[row];
+    const int key_lo = first_key_of(pos, mask_kind, mask_size);
+    const int tiles = (pos - key_lo) / KT + 1;
+    const int64_t page_elems = (int64_t)kv_heads * page_size * (D + DV);
+    const bf16* kbase = cache + (int64_t)kv_head * page_size * D;
+    const bf16* vbase = cache + (int64_t)kv_heads * page_size * D + (int64_t)kv_head * page_size * DV;
+    const int* table = block_table + (int64_t)seq * bt_stride;
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(tile_smem);
+    const int copy_row = tid >> 1, copy_half = tid & 1;
+    auto fill = [&](int tile) {
+        const uint32_t stage = smem_base + (uint32_t)(tile & 1) * STAGE;
+        const int key = key_lo + tile * KT + copy_row;
+        const bool there = key <= pos;
+        const int k = there ? key : pos;
+        const int64_t base = (int64_t)table[k / page_size] * page_elems;
+        const int in_page = k % page_size;
+        const bf16* kp = kbase + base + (int64_t)in_page * D;
+        const bf16* vp = vbase + base + (int64_t)in_page * DV;
+        const int bytes = there ? 16 : 0;
+        constexpr int KC = D / 8, VC = DV / 8;
+#pragma unroll
+        for (int c = 0; c < (KC + 1) / 2; ++c) {
+            const int chunk = copy_half * ((KC + 1) / 2) + c;
+            if (chunk < KC) cp_async16(stage + copy_row * KS + chunk * 16, kp + chunk * 8, bytes);
+        }
+#pragma unroll
+        for (int c = 0; c < (VC + 1) / 2; ++c) {
+            const int chunk = copy_half * ((VC + 1) / 2) + c;
+            if (chunk < VC) cp_async16(stage + KT * KS + copy_row * VS + chunk * 16, vp + chunk * 8, bytes);
+        }
+    };
+    fill(0);
+    cp_async_commit();
+    uint32_t qa[D / 16][4];
+    {
+        const bool top_there = g < per, bottom_there = g + 8 < per;
+        const bf16* top = q + (int64_t)row * q_stride + (int64_t)(kv_head * per + g) * D;
+        const bf16* bottom = top + 8 * D;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            qa[ks][0] = top_there ? *reinterpret_cast<const uint32_t*>(top + ks * 16 + 2 * t) : 0u;
+            qa[ks][1] = bottom_there ? *reinterpret_cast<const uint32_t*>(bottom + ks * 16 + 2 * t) : 0u;
+            qa[ks][2] = top_there ? *reinterpret_cast<const uint32_t*>(top + ks * 16 + 2 * t + 8) : 0u;
+            qa[ks][3] = bottom_there ? *reinterpret_cast<const uint32_t*>(bottom + ks * 16 + 2 * t + 8) : 0u;
+        }
+    }
+    float m[2] = {-1.0e30f, -1.0e30f}, l[2] = {0.0f, 0.0f};
+    float o[DV / 8][4];
+#pragma unroll
+    for (int j = 0; j < DV / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[j][e] = 0.0f;
+    for (int tile = 0; tile < tiles; ++tile) {
+        if (tile + 1 < tiles) {
+            fill(tile + 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t kstage = smem_base + (uint32_t)(tile & 1) * STAGE, vstage = kstage + KT * KS;
+        const int key0 = key_lo + tile * KT + warp * 16;         // the warp's 16 keys of the tile
+        if (key0 <= pos) {
+            float s[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[j][e] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                uint32_t b[4];
+                ldmatrix_x4(b, kstage + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * KS + (ks * 2 + ((lane >> 3) & 1)) * 16);
+                mma_bf16_16816(s[0], qa[ks], b);
+                mma_bf16_16816(s[1], qa[ks], b + 2);
+            }
+            float top[2] = {-1.0e30f, -1.0e30f};
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + j * 8 + 2 * t + (e & 1);
+                    s[j][e] = key <= pos ? s[j][e] * scale : -1.0e30f;      // (every key from key_lo on is inside the mask)
+                    top[e >> 1] = fmaxf(top[e >> 1], s[j][e]);
+                }
+            float corr[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 1));
+                top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 2));
+                const float m_new = fmaxf(m[r], top[r]);
+                corr[r] = __expf(m[r] - m_new);
+                m[r] = m_new;
+                l[r] *= corr[r];
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p = s[j][e] > -1.0e29f ? __expf(s[j][e] - m[e >> 1]) : 0.0f;
+                    s[j][e] = p;
+                    l[e >> 1] += p;
+                }
+#pragma unroll
+            for (int j = 0; j < DV / 8; ++j) {
+                o[j][0] *= corr[0]; o[j][1] *= corr[0];
+                o[j][2] *= corr[1]; o[j][3] *= corr[1];
+            }
+            uint32_t hi[4], lo[4];
+            split_bf16(s[0][0], s[0][1], hi[0], lo[0]);
+            split_bf16(s[0][2], s[0][3], hi[1], lo[1]);
+            split_bf16(s[1][0], s[1][1], hi[2], lo[2]);
+            split_bf16(s[1][2], s[1][3], hi[3], lo[3]);
+#pragma unroll
+            for (int jp = 0; jp < DV / 16; ++jp) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vstage + (warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * VS + (jp * 2 + (lane >> 4)) * 16);
+                mma_bf16_16816(o[2 * jp], hi, b);
+                mma_bf16_16816(o[2 * jp], lo, b);
+                mma_bf16_16816(o[2 * jp + 1], hi, b + 2);
+                mma_bf16_16816(o[2 * jp + 1], lo, b + 2);
+            }
+        }
+        __syncthreads();
+    }
+    // the warps' partial results, then their sum in warp order
+    float* parts = reinterpret_cast<float*>(tile_smem + 2 * STAGE);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        float* mine = parts + ((size_t)warp * 16 + g + r * 8) * PART;
+#pragma unroll
+        for (int j = 0; j < DV / 8; ++j) {
+            mine[j * 8 + 2 * t] = o[j][2 * r];
+            mine[j * 8 + 2 * t + 1] = o[j][2 * r + 1];
+        }
+        if (t == 0) {
+            mine[DV] = m[r];
+            mine[DV + 1] = l[r];
+        }
+    }
+    __syncthreads();
+    for (int index = tid; index < per * DV; index += 128) {
+        const int head_row = index / DV, col = index % DV;
+        float top = -1.0e30f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) top = fmaxf(top, parts[((size_t)w * 16 + head_row) * PART + DV]);
+        float total = 0.0f, value = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* theirs = parts + ((size_t)w * 16 + head_row) * PART;
+            const float weight = __expf(theirs[DV] - top);
+            total = fmaf(theirs[DV + 1], weight, total);
+            value = fmaf(theirs[col], weight, value);
+        }
+        out[(int64_t)row * out_stride + (int64_t)(kv_head * per + head_row) * DV + col] =
+            __float2bfloat16_rn(value / fmaxf(total, 1.0e-30f));
+    }
+}
+
+template <int D, int DV>
+int launch_rows(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache, const int* positions,
+                const int* seq_of_row, const int* block_table, int bt_stride, int rows, int heads, int kv_heads,
+                int page_size, int mask_kind, int mask_size, float scale, cudaStream_t stream) {
+    constexpr int smem = 2 * KT * (D * 2 + 16 + DV * 2 + 16) + 4 * 16 * (DV + 2) * 4;
+    auto kernel = attention_rows_kernel<D, DV>;
+    if (smem > 40 * 1024) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (err != cudaSuccess) return (int)err;
+    }
+    cudaError_t launched = tb_launch_pdl(kernel, dim3(rows, kv_heads), dim3(128), (size_t)smem, stream, (const bf16*)q,
+                                         q_stride, (bf16*)out, out_stride, (const bf16*)cache, positions, seq_of_row,
+                                         block_table, bt_stride, heads, kv_heads, page_size, mask_kind, mask_size, scale);
+    return launched == cudaSuccess ? tb_launch_status() : (int)launched;
+}
+
 template <int D, int DV>
 int launch(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache, const int* positions,
            const int* row_start, const int* block_table, int bt_stride, int rows, int num_seqs, int heads, int kv_heads,
@@ -302,4 +497,28 @@ TB_EXPORT int tb_attention_prompt_mma(const void* q, int64_t q_stride, void* out
     if (dim == 128 && vdim == 64) TB_ATTEND(128, 64);
     TB_ATTEND(128, 128);
 #undef TB_ATTEND
+}
+
+// The same attention for steps of few rows: one block a (row, kv head), any positions.  At most 16 query heads a kv
+// head; seq_of_row: int32 [rows].
+TB_EXPORT int tb_attention_rows_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride, const void* cache,
+                                    const int* positions, const int* seq_of_row, const int* block_table, int bt_stride,
+                                    int rows, int heads, int kv_heads, int dim, int vdim, int page_size, int mask_kind,
+                                    int mask_size, float scale, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (!tb_attention_prompt_mma_supported(dim, vdim)) return TB_ERR_BAD_SIZE;
+    if (kv_heads < 1 || heads < 1 || heads % kv_heads != 0 || heads / kv_heads > 16 || page_size < 1) return TB_ERR_BAD_SIZE;
+    if (kv_heads > 65535) return TB_ERR_BAD_SIZE;
+    if (mask_kind < MASK_CAUSAL || mask_kind > MASK_BLOCKS) return TB_ERR_BAD_SIZE;
+    if (mask_kind != MASK_CAUSAL && mask_size < 1) return TB_ERR_BAD_SIZE;
+    if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) % 16 != 0 || q_stride % 2 != 0) return TB_ERR_BAD_ALIGN;
+#define TB_ROWS(D, DV)                                                                                              \
+    return launch_rows<D, DV>(q, q_stride, out, out_stride, cache, positions, seq_of_row, block_table, bt_stride,   \
+                              rows, heads, kv_heads, page_size, mask_kind, mask_size, scale, stream)
+    if (dim == 64 && vdim == 48) TB_ROWS(64, 48);
+    if (dim == 64 && vdim == 64) TB_ROWS(64, 64);
+    if (dim == 64 && vdim == 128) TB_ROWS(64, 128);
+    if (dim == 128 && vdim == 64) TB_ROWS(128, 64);
+    TB_ROWS(128, 128);
+#undef TB_ROWS
 }

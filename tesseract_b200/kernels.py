@@ -862,6 +862,24 @@ def attention_prompt_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
     return out
 
 
+def attention_rows_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
+                       seq_of_row: torch.Tensor, block_table: torch.Tensor, *, heads: int, kv_heads: int, dim: int,
+                       vdim: int, page_size: int, mask_kind: int, mask_size: int, scale: float) -> torch.Tensor:
+    """:func:`attention_prompt_mma` for steps of few rows at any positions: a block a (row, kv head), the kv head's
+    query heads (at most 16) side by side in the tensor-core tile."""
+    _cuda(q, out, cache, positions, seq_of_row, block_table)
+    rows = q.shape[0]
+    _need(q.dtype == torch.bfloat16 and q.stride(1) == 1 and q.shape[1] == heads * dim, "attention_rows_mma q")
+    _need(out.stride(1) == 1 and out.shape == (rows, heads * vdim) and out.dtype == q.dtype, "attention_rows_mma out")
+    _need(cache.dtype == q.dtype and cache.is_contiguous(), "attention_rows_mma cache")
+    lib = load_library("attention_prompt_mma")
+    _check(lib.tb_attention_rows_mma(_ptr(q), _i64(q.stride(0)), _ptr(out), _i64(out.stride(0)), _ptr(cache),
+                                     _ptr(positions), _ptr(seq_of_row), _ptr(block_table), _i32(block_table.stride(0)),
+                                     _i32(rows), _i32(heads), _i32(kv_heads), _i32(dim), _i32(vdim), _i32(page_size),
+                                     _i32(mask_kind), _i32(mask_size), _f32(scale), _stream()), "attention_rows_mma")
+    return out
+
+
 def gated_recurrence(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor,
                      out: torch.Tensor, row_start: torch.Tensor, state_slots: torch.Tensor, *, num_seqs: int,
                      max_new: int) -> torch.Tensor:

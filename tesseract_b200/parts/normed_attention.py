@@ -120,7 +120,14 @@ class NormedAttention(Mixer):
                                 dim=self.key_dim, vdim=self.value_dim, rot_dims=self.rot_dims,
                                 unit_norm=self.unit_norm, eps=self.qk_norm_eps, page_size=cache.page_size)
         attended = torch.empty((rows, self.o_width), dtype=proj.dtype, device=proj.device)
-        if plan.masked_attention(proj.dtype, rows, self.key_dim, self.value_dim) == "attention_prompt_mma":
+        choice = plan.masked_attention(proj.dtype, rows, self.key_dim, self.value_dim,
+                                       heads_per_kv=self.num_heads // self.num_kv_heads)
+        if choice == "attention_rows_mma":
+            kernels.attention_rows_mma(q, attended, cache.storage, ctx.positions, ctx.seq_of_row, group.block_table,
+                                       heads=self.num_heads, kv_heads=self.num_kv_heads, dim=self.key_dim,
+                                       vdim=self.value_dim, page_size=cache.page_size, mask_kind=_MASKS[self.mask_kind],
+                                       mask_size=self.mask_size, scale=self.scale)
+        elif choice == "attention_prompt_mma":
             kernels.attention_prompt_mma(q, attended, cache.storage, ctx.positions, ctx.row_start, group.block_table,
                                          num_seqs=ctx.num_seqs, heads=self.num_heads, kv_heads=self.num_kv_heads,
                                          dim=self.key_dim, vdim=self.value_dim, page_size=cache.page_size,

@@ -145,14 +145,17 @@ def _prompt_mma_takes(dtype: torch.dtype, key_dim: int, value_dim: int) -> bool:
 
 
 def masked_attention(dtype: torch.dtype, rows: int, key_dim: int, value_dim: int, sink: bool = False,
-                     gated: bool = False) -> str:
-    """The kernel for attention with 32-bit scores and weights over keys and values of separate widths:
-    ``"attention_prompt_mma"`` (tensor cores; bfloat16, no sink, no gate, head sizes it is built for) for steps of
-    more than 256 rows, where ``attention_masked`` stops sharing a row's keys between warps: 2,048 rows of 32 heads
-    of 64 under a window of 512 take 555 us there.  ``"attention_masked"`` otherwise."""
-    if (rows >= MASKED_PROMPT_MIN_ROWS and not sink and not gated and dtype == torch.bfloat16
-            and _prompt_mma_takes(dtype, key_dim, value_dim)):
-        return "attention_prompt_mma"
+                     gated: bool = False, heads_per_kv: int = 1) -> str:
+    """The kernel for attention with 32-bit scores and weights over keys and values of separate widths.  On the
+    tensor cores (bfloat16, no sink, no gate, head sizes the kernels are built for): ``"attention_prompt_mma"`` for
+    steps of more than 256 rows (2,048 rows of 32 heads of 64 under a window of 512: 87 us against 555 for
+    ``attention_masked``), ``"attention_rows_mma"`` for steps of fewer (a block a row and kv head; at most 16 query
+    heads a kv head).  ``"attention_masked"`` otherwise."""
+    if not sink and not gated and dtype == torch.bfloat16 and _prompt_mma_takes(dtype, key_dim, value_dim):
+        if rows >= MASKED_PROMPT_MIN_ROWS:
+            return "attention_prompt_mma"
+        if heads_per_kv <= 16:
+            return "attention_rows_mma"
     return "attention_masked"
 
 
@@ -308,6 +311,9 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
                 lines.append(f"    mixer    '{mixer.kind}' (its own kernels between the products)")
                 for name, linear, epilogue in mixer.products():
                     lines.append(f"      {name:10s} {product(dtype, rows, linear.out_features, linear.in_features, epilogue=epilogue)}")
+                if hasattr(mixer, "key_dim") and hasattr(mixer, "value_dim") and not hasattr(mixer, "taps"):
+                    per = mixer.num_heads // mixer.num_kv_heads
+                    lines.append(f"      attend     {masked_attention(dtype, rows, mixer.key_dim, mixer.value_dim, heads_per_kv=per)}")
             else:
                 lines.append(f"    mixer    '{mixer.kind}' (its own code)")
             if isinstance(ffn, SwiGLU):
@@ -322,6 +328,12 @@ def describe(model, row_counts: Sequence[int] = (1, 8, 16, 17, 64, 512, 2048), c
                     lines.append(f"      {name:10s} {product(dtype, rows, linear.out_features, linear.in_features, epilogue=epilogue)}")
             elif ffn is not None:
                 lines.append(f"    feed-forward '{ffn.kind}' (its own code)")
+    for index, injection in enumerate(getattr(model, "injections", ())):
+        entries = [i for i, entry in enumerate(model.spec.run_order) if entry.inject == index]
+        lines.append(f"injection '{injection.kind}' in front of run entries {entries}")
+        for rows in row_counts:
+            for name, linear, epilogue in (injection.products() if hasattr(injection, "products") else []):
+                lines.append(f"  {rows} rows  {name:10s} {product(dtype, rows, linear.out_features, linear.in_features, epilogue=epilogue)}")
     proj = getattr(model.head, "proj", None)
     if proj is not None:
         lines.append("head (wanted rows only)")

@@ -126,3 +126,19 @@ def test_attention_plans():
                              page_size=16, sms=SMS)
     assert grouped.prompt is not None and not grouped.split and not grouped.fused_decode
     assert plan.attention(F32, new_tokens=[1, 7], max_context=100, **sizes).rows
+
+
+def test_masked_attention_goes_to_the_tensor_cores_for_many_bfloat16_rows_of_sizes_it_takes():
+    import torch
+
+    from tesseract_b200 import plan
+
+    assert plan.masked_attention(torch.bfloat16, 2048, 64, 64) == "attention_prompt_mma"
+    assert plan.masked_attention(torch.bfloat16, 257, 128, 128) == "attention_prompt_mma"
+    assert plan.masked_attention(torch.bfloat16, 256, 64, 64, heads_per_kv=4) == "attention_rows_mma"
+    assert plan.masked_attention(torch.bfloat16, 8, 128, 64, heads_per_kv=16) == "attention_rows_mma"
+    assert plan.masked_attention(torch.bfloat16, 8, 64, 64, heads_per_kv=32) == "attention_masked"   # more heads than a tile has rows
+    assert plan.masked_attention(torch.float32, 2048, 64, 64) == "attention_masked"          # the true 32-bit path
+    assert plan.masked_attention(torch.bfloat16, 2048, 40, 64) == "attention_masked"         # a head size it is not built for
+    assert plan.masked_attention(torch.bfloat16, 2048, 64, 64, sink=True) == "attention_masked"
+    assert plan.masked_attention(torch.bfloat16, 2048, 64, 64, gated=True) == "attention_masked"

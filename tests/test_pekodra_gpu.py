@@ -327,7 +327,7 @@ def test_tensor_core_prompt_attention_against_plain_and_the_row_kernel(d, dv, ki
     keys before them were stored by earlier steps), and a single row at position 40; pages in scrambled order."""
     from tesseract_b200 import kernels
 
-    heads, kv_heads, page = 4, 2, 16
+    heads, kv_heads, page = (4, 2, 16) if d == 64 else (12, 1, 16)   # (twelve query heads on one kv head: both halves of a tile)
     scale = 4.0 / d ** 0.5                                           # sharp softmaxes: the weights matter
     spans = [(0, 300), (500, 70), (40, 1)]                           # (first position, rows) of each sequence's portion
     g = torch.Generator().manual_seed(d + dv + size)
@@ -371,8 +371,14 @@ def test_tensor_core_prompt_attention_against_plain_and_the_row_kernel(d, dv, ki
     kernels.attention_masked(q_all, None, other, storage.to(dev()), positions, seq_of_row, table.to(dev()), heads=heads,
                              kv_heads=kv_heads, dim=d, vdim=dv, page_size=page, mask_kind=mask_kind, mask_size=size,
                              sink=False, scale=scale)
+    single = torch.empty_like(got)                                   # the kernel for steps of few rows takes any rows
+    kernels.attention_rows_mma(q_all, single, storage.to(dev()), positions, seq_of_row, table.to(dev()), heads=heads,
+                               kv_heads=kv_heads, dim=d, vdim=dv, page_size=page, mask_kind=mask_kind, mask_size=size,
+                               scale=scale)
     assert (got.cpu().double() - want).abs().max().item() <= 2e-2          # the output's own rounding to bfloat16
     assert (got.float() - other.float()).abs().max().item() <= 2e-2
+    assert (single.cpu().double() - want).abs().max().item() <= 2e-2
+    assert ((single.cpu().double() - want).abs() <= 1e-2 * want.abs() + 1e-3).all()
     # the weights are 32-bit: an output far below the largest one keeps its relative accuracy
     assert ((got.cpu().double() - want).abs() <= 1e-2 * want.abs() + 1e-3).all()
 
