@@ -708,8 +708,8 @@ def pekodra_config(size, layers):
         stored, start, stop = layers, 0, 0
     mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
              "mask": {"size": p["window"]}, "scale": z["dim"] ** -0.5,
-             "rot": {"dims": p["rot_dims"], "base": 1000000.0,
-                     "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+             "rot": {"dims": p["rot_dims"], "base": 500000.0,
+                     "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
     dense = {"kind": "dense", "ff": p["dense_ff"]}
     moe = {"kind": "moe", "router": {"experts": p["experts"], "top": p["top"]}, "expert": {"ff": p["expert_ff"]},
            "shared": {"ff": p["shared_ff"]}}
@@ -942,7 +942,7 @@ def pekodra_kernels(size, pk):
     H, G, d, W = z["heads"], z["kv_heads"], z["dim"], z["width"]
     F, E, top, EF, window, page = p["dense_ff"], p["experts"], p["top"], p["expert_ff"], p["window"], PAGE_SIZE
     channels = H * d + 2 * G * d
-    freqs, amplitude = blended_inverse_frequencies(p["rot_dims"], 1e6, {"factor": 4.0, "original": 2048, "fast": 32.0,
+    freqs, amplitude = blended_inverse_frequencies(p["rot_dims"], 5e5, {"factor": 8.0, "original": 8192, "fast": 32.0,
                                                                        "slow": 1.0})
     inv_freq = torch.tensor(freqs, dtype=torch.float32, device=dev)
     SETS = 8

@@ -52,7 +52,7 @@ TINY_PEKODRA = {
                      layer(attention(3, 1, 6, 12, 9, (6, 3.0, None), 0.5), dense(30))]},
     # a single walk of a loop that is the last layer alone; a window of one position
     "d": {"architecture": "Pekodra", "width": 32, "vocab": 64, "norm": {"eps": 1e-6}, "embedding": {"scale": 4.0},
-          "logit_scale": 0.25, "loop": {"start": 1, "stop": 2, "times": 1},
+          "logit_scale": 0.125, "loop": {"start": 1, "stop": 2, "times": 1},
           "layers": [layer(attention(2, 2, 8, 8, 1, (8, 20.0, None), 0.4), dense(16)),
                      layer(attention(4, 1, 16, 8, 17, (12, 500.0, (16.0, 8, 1.0, 0.25)), 0.2), moe(9, 4, 8, 16))]},
     # head sizes and prompt lengths that send prompt portions to the tensor-core attention: a window, and all keys
@@ -80,23 +80,23 @@ def random_config(seed: int) -> dict:
         if r.random() < 0.85:
             scaling = None
             if r.random() < 0.6:
-                scaling = (r.choice([2.0, 4.0, 10.0]), r.choice([16, 64, 2048]), r.choice([32.0, 8.0, 2.0]),
+                scaling = (r.choice([2.0, 4.0, 10.0]), r.choice([16, 64, 1024]), r.choice([32.0, 8.0, 2.0]),
                            r.choice([1.0, 0.5]))
-            rot = (r.choice(range(2, dim + 1, 2)), r.choice([10.0, 1000.0, 1000000.0]), scaling)
+            rot = (r.choice(range(2, dim + 1, 2)), r.choice([10.0, 1000.0, 500000.0]), scaling)
         window = r.choice([None, 1, 3, 16, 17, 50, 64, 120, 500])
         kind = r.random()
         if kind < 0.4:
             mlp = dense(r.choice([8, 40, 100, 256]))
         elif kind < 0.85:
-            experts = r.choice([2, 3, 8, 16, 33])
+            experts = r.choice([2, 3, 8, 12, 33])
             mlp = moe(experts, r.randint(1, min(experts, 4)), r.choice([8, 24, 32, 64, 96]),
-                      r.choice([None, 16, 48, 128]))
+                      r.choice([None, 16, 48, 96]))
         else:
             mlp = None
         layers.append(layer(attention(heads, kv_heads, dim, vdim, window, rot, r.choice([dim ** -0.5, 0.3, 0.07])), mlp))
     config = {"architecture": "Pekodra", "width": width, "vocab": r.randint(40, 700),
-              "norm": {"eps": r.choice([1e-5, 1e-6])}, "embedding": {"scale": r.choice([1.0, 3.0, 0.5])},
-              "logit_scale": r.choice([1.0, 0.25, 1.7]), "layers": layers}
+              "norm": {"eps": r.choice([1e-5, 1e-6])}, "embedding": {"scale": r.choice([1.0, 2.0, 0.5])},
+              "logit_scale": r.choice([1.0, 0.5, 1.7]), "layers": layers}
     if r.random() < 0.8:
         start = r.randint(0, len(layers) - 1)
         config["loop"] = {"start": start, "stop": r.randint(start + 1, len(layers)), "times": r.randint(1, 3)}

@@ -57,9 +57,9 @@ def test_the_loop_repeats_its_layers_in_a_row():
     from tesseract_b200.models.pekodra_config import PekodraConfig
 
     config = copy.deepcopy(TINY_PEKODRA["a"])
-    config["loop"] = {"start": 1, "stop": 3, "times": 3}
+    config["loop"] = {"start": 2, "stop": 4, "times": 3}
     order = PekodraConfig.from_dict(config).run_order()
-    assert order == ((0, False), (1, True), (2, False), (1, True), (2, False), (1, True), (2, False), (3, False))
+    assert order == ((0, False), (1, False), (2, True), (3, False), (2, True), (3, False), (2, True), (3, False))
     config["loop"] = {"start": 0, "stop": 4, "times": 2}
     assert [i for i, _ in PekodraConfig.from_dict(config).run_order()] == [0, 1, 2, 3, 0, 1, 2, 3]
     del config["loop"]
@@ -100,7 +100,7 @@ def test_random_configurations_describe_and_write(tmp_path, seed):
 def test_blended_frequencies_agree_with_the_plain_recipe():
     from tesseract_b200.parts.rotary import blended_inverse_frequencies
 
-    for dims, base, scaling in [(64, 1e6, {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}),
+    for dims, base, scaling in [(64, 5e5, {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}),
                                 (8, 1000.0, {"factor": 3.0, "original": 64, "fast": 8.0, "slow": 1.0}),
                                 (12, 500.0, {"factor": 16.0, "original": 8, "fast": 1.0, "slow": 0.25}),
                                 (10, 30.0, None)]:
@@ -109,8 +109,8 @@ def test_blended_frequencies_agree_with_the_plain_recipe():
         assert amplitude == pytest.approx(want_amplitude, rel=1e-12)
         assert list(got) == pytest.approx(want, rel=1e-12)
     # with a stretch, the fastest frequencies stay and the slowest are divided by the factor
-    got, _ = blended_inverse_frequencies(64, 1e6, {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0})
-    assert got[0] == 1.0 and got[-1] == pytest.approx(1e6 ** (-62 / 64) / 4.0)
+    got, _ = blended_inverse_frequencies(64, 5e5, {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0})
+    assert got[0] == 1.0 and got[-1] == pytest.approx(5e5 ** (-62 / 64) / 8.0)
 
 
 def test_a_window_gives_pages_back_while_the_request_lives():

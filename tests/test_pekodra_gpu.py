@@ -120,10 +120,10 @@ def test_scaled_embedding_and_the_scaled_head(dtype):
     tokens = torch.tensor([3, 29, 0, 3], dtype=torch.int32, device=dev())
     got = part.forward(tokens)
     assert got.dtype == torch.float32 and torch.equal(got.cpu(), table.float()[[3, 29, 0, 3]] * 2.5)
-    head_spec = PartSpec.make("lm_head", {"vocab_size": 30, "hidden_size": 24, "scale": 0.25}, {"weight": "h"})
+    head_spec = PartSpec.make("lm_head", {"vocab_size": 30, "hidden_size": 24, "scale": 0.375}, {"weight": "h"})
     head = HEADS.get(head_spec.kind)(head_spec, {"weight": table}, runtime(dtype))
     x = torch.randn(5, 24, generator=g).to(dtype)
-    want = (x.double() @ table.double().T) * 0.25
+    want = (x.double() @ table.double().T) * 0.375
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     assert torch.allclose(head.forward(x.to(dev())).cpu().double(), want, rtol=tol, atol=tol)
 
@@ -223,7 +223,7 @@ def _step_context(positions, page_order, page):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv_heads,d,dv", [(4, 2, 16, 24), (6, 2, 64, 48), (3, 1, 20, 12), (4, 1, 64, 64),
+@pytest.mark.parametrize("heads,kv_heads,d,dv", [(4, 2, 16, 24), (8, 2, 64, 48), (3, 1, 20, 12), (4, 1, 64, 64),
                                                  (2, 2, 128, 128), (2, 1, 64, 128), (2, 1, 128, 64)])
 @pytest.mark.parametrize("window", [33, 16, 5, 1, None])
 def test_window_attention_sees_exactly_its_keys(dtype, heads, kv_heads, d, dv, window):
@@ -409,7 +409,7 @@ def _experts_part(dtype, width, experts, top, size, shared, seed):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width,experts,top,size,shared", [(64, 3, 2, 32, 48), (40, 5, 1, 24, None), (96, 16, 3, 64, 128),
+@pytest.mark.parametrize("width,experts,top,size,shared", [(64, 3, 2, 32, 48), (40, 5, 1, 24, None), (96, 12, 3, 64, 160),
                                                            (32, 4, 4, 8, 16), (66, 7, 2, 20, 10), (256, 6, 2, 320, 64)])
 @pytest.mark.parametrize("rows", [1, 9, 300])
 def test_routed_experts_alone(dtype, width, experts, top, size, shared, rows):
