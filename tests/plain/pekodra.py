@@ -36,6 +36,14 @@ def load_folder(model_dir: str):
 
 
 # ----------------------------------------------------------------------------- mechanisms
+# ``round_to`` (None or a torch dtype): where a serving path would store an activation in a 16-bit format (the
+# operands of every product, stored queries, keys and values), the value is rounded to that format and widened
+# again.  The difference to the unrounded run is the noise that such rounding alone causes; sums that the design
+# keeps in 32-bit (the stream, scores and weights, norms' statistics, router logits) are never rounded.
+
+
+def rounded(x: torch.Tensor, round_to) -> torch.Tensor:
+    return x if round_to is None else x.to(round_to).to(x.dtype)
 
 
 def unit_rms(x: torch.Tensor, eps: float) -> torch.Tensor:
@@ -99,18 +107,18 @@ def window_mask(T: int, window: Optional[int]) -> torch.Tensor:
     return seen
 
 
-def window_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Mapping, eps: float) -> torch.Tensor:
+def window_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Mapping, eps: float, round_to=None) -> torch.Tensor:
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ w["q"].T).reshape(T, H, d)
-    k = (h @ w["k"].T).reshape(T, G, d)
-    v = (h @ w["v"].T).reshape(T, G, dv)
+    q = rounded(h @ w["q"].T, round_to).reshape(T, H, d)
+    k = rounded(h @ w["k"].T, round_to).reshape(T, G, d)
+    v = rounded(h @ w["v"].T, round_to).reshape(T, G, dv)
     rot = m.get("rot")
     if rot and rot.get("dims"):
         freqs, amplitude = blended_frequencies(rot["dims"], float(rot["base"]), rot.get("scaling"))
         q = rotate_half(q, range(T), rot["dims"], freqs, amplitude)
         k = rotate_half(k, range(T), rot["dims"], freqs, amplitude)
-    q, k = unit_rms(q, eps), unit_rms(k, eps)
+    q, k = rounded(unit_rms(q, eps), round_to), rounded(unit_rms(k, eps), round_to)
     seen = window_mask(T, (m.get("mask") or {}).get("size"))
     out = torch.zeros(T, H, dv, dtype=h.dtype)
     for head in range(H):
@@ -118,17 +126,17 @@ def window_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Mapping,
         scores = (q[:, head] @ k[:, g].T) * float(m["scale"])
         scores = scores.masked_fill(~seen, float("-inf"))
         out[:, head] = torch.softmax(scores, dim=-1) @ v[:, g]
-    return out.reshape(T, H * dv) @ w["o"].T
+    return rounded(out.reshape(T, H * dv), round_to) @ w["o"].T
 
 
-def gated_mlp(h: torch.Tensor, w: Mapping[str, torch.Tensor]) -> torch.Tensor:
-    gate = h @ w["gate"].T + w["gate.b"]
-    up = h @ w["up"].T + w["up.b"]
-    return (gelu_tanh(gate) * up) @ w["down"].T + w["down.b"]
+def gated_mlp(h: torch.Tensor, w: Mapping[str, torch.Tensor], round_to=None) -> torch.Tensor:
+    gate = rounded(h @ w["gate"].T, round_to) + w["gate.b"]
+    up = rounded(h @ w["up"].T, round_to) + w["up.b"]
+    return rounded(gelu_tanh(gate) * up, round_to) @ w["down"].T + w["down.b"]
 
 
-def squared_relu_expert(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
-    return (torch.relu(h @ up.T) ** 2) @ down.T
+def squared_relu_expert(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, round_to=None) -> torch.Tensor:
+    return rounded(torch.relu(rounded(h @ up.T, round_to)) ** 2, round_to) @ down.T
 
 
 def route(h: torch.Tensor, router: torch.Tensor, top: int):
@@ -139,11 +147,11 @@ def route(h: torch.Tensor, router: torch.Tensor, top: int):
 
 
 def expert_mixture(h: torch.Tensor, w: Mapping[str, torch.Tensor], mlp: Mapping, chosen: Optional[torch.Tensor] = None,
-                   report: Optional[list] = None) -> torch.Tensor:
+                   report: Optional[list] = None, round_to=None) -> torch.Tensor:
     """``chosen`` (``[T, top]``) overrides the router's choice (the weights are still the softmax over the chosen
     logits): a comparison with an implementation in lower precision then does not hang on which of two nearly equal
     logits it found larger.  ``report`` receives ``(own choice [T, top], margin [T])``, the margin being the distance
-    between the last chosen and the first rejected logit over the spread of the row's logits."""
+    between the last chosen and the first rejected logit over the root mean square of all the run's logits."""
     experts, top = mlp["router"]["experts"], mlp["router"]["top"]
     own, weights = route(h, w["router"], top)
     if report is not None or chosen is not None:
@@ -151,7 +159,7 @@ def expert_mixture(h: torch.Tensor, w: Mapping[str, torch.Tensor], mlp: Mapping,
         ranked = torch.sort(logits, dim=-1, descending=True).values
         margin = (ranked[:, top - 1] - ranked[:, top]) if top < experts else torch.full((h.shape[0],), float("inf"))
         if report is not None:
-            report.append((own, margin / (logits.std(dim=-1) + 1e-30)))
+            report.append((own, margin / (logits.pow(2).mean().sqrt() + 1e-30)))
         if chosen is not None:
             chosen = chosen.long()
             weights = torch.softmax(torch.gather(logits, 1, chosen), dim=-1)
@@ -161,9 +169,9 @@ def expert_mixture(h: torch.Tensor, w: Mapping[str, torch.Tensor], mlp: Mapping,
     for t in range(h.shape[0]):
         for slot in range(top):
             e = int(chosen[t, slot])
-            out[t] += weights[t, slot] * squared_relu_expert(h[t:t + 1], w[f"e{e}.up"], w[f"e{e}.down"])[0]
+            out[t] += weights[t, slot] * squared_relu_expert(h[t:t + 1], w[f"e{e}.up"], w[f"e{e}.down"], round_to)[0]
     if mlp.get("shared"):
-        out = out + squared_relu_expert(h, w["shared.up"], w["shared.down"])
+        out = out + squared_relu_expert(h, w["shared.up"], w["shared.down"], round_to)
     return out
 
 
@@ -189,10 +197,10 @@ def _sub(tensors: Mapping[str, torch.Tensor], prefix: str, dtype) -> Dict[str, t
 
 def forward(config: Mapping, tensors: Mapping[str, torch.Tensor], tokens: Sequence[int], dtype=torch.float64,
             keep_layers: bool = False, routing: Optional[Mapping[int, torch.Tensor]] = None,
-            report: Optional[list] = None):
+            report: Optional[list] = None, round_to=None):
     """Logits ``[T, vocab]`` of a whole sequence (and, with ``keep_layers``, the stream after every layer run).
     ``routing[n]`` (``[T, top]``) fixes the experts of the n-th run of a layer with experts; ``report`` receives the
-    model's own choice and its margin for every such run (see :func:`expert_mixture`)."""
+    model's own choice and its margin for every such run (see :func:`expert_mixture`).  ``round_to``: see above."""
     routed_runs = 0
     eps = float(config["norm"]["eps"])
     x0 = tensors["embed"].to(dtype)[list(tokens)] * float(config["embedding"]["scale"])
@@ -200,24 +208,24 @@ def forward(config: Mapping, tensors: Mapping[str, torch.Tensor], tokens: Sequen
     after = []
     for index, starts in run_order(config):
         if starts:
-            x = torch.cat([x, x0], dim=-1) @ tensors["loop.in"].to(dtype).T
+            x = rounded(torch.cat([x, x0], dim=-1), round_to) @ tensors["loop.in"].to(dtype).T
         layer = config["layers"][index]
         prefix = f"l{index}."
-        mixed = window_attention(offset_rms_norm(x, tensors[prefix + "norm1"].to(dtype), eps),
-                                 _sub(tensors, prefix + "mix.", dtype), layer["mixer"], eps)
+        mixed = window_attention(rounded(offset_rms_norm(x, tensors[prefix + "norm1"].to(dtype), eps), round_to),
+                                 _sub(tensors, prefix + "mix.", dtype), layer["mixer"], eps, round_to)
         mlp = layer.get("mlp")
         if mlp:
-            h2 = offset_rms_norm(x, tensors[prefix + "norm2"].to(dtype), eps)
+            h2 = rounded(offset_rms_norm(x, tensors[prefix + "norm2"].to(dtype), eps), round_to)
             w = _sub(tensors, prefix + "mlp.", dtype)
             if mlp["kind"] == "dense":
-                fed = gated_mlp(h2, w)
+                fed = gated_mlp(h2, w, round_to)
             else:
-                fed = expert_mixture(h2, w, mlp, None if routing is None else routing[routed_runs], report)
+                fed = expert_mixture(h2, w, mlp, None if routing is None else routing[routed_runs], report, round_to)
                 routed_runs += 1
             x = x + (mixed + fed)
         else:
             x = x + mixed
         after.append(x)
-    final = offset_rms_norm(x, tensors["final.norm"].to(dtype), eps)
+    final = rounded(offset_rms_norm(x, tensors["final.norm"].to(dtype), eps), round_to)
     logits = (final @ tensors["head"].to(dtype).T) * float(config["logit_scale"])
     return (logits, torch.stack(after)) if keep_layers else logits
