@@ -835,9 +835,9 @@ def attention_masked(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
 
 
 def attention_prompt_mma_supported(dtype: torch.dtype, dim: int, vdim: int) -> bool:
-    """Whether the tensor-core prompt attention takes these head sizes (bfloat16 only)."""
-    return dtype == torch.bfloat16 and bool(load_library("attention_prompt_mma").tb_attention_prompt_mma_supported(
-        _i32(dim), _i32(vdim)))
+    """Whether the tensor-core attention kernels take these head sizes (bfloat16 only; the sizes they are instantiated
+    for, as ``tb_attention_prompt_mma_supported`` of the library says too: asked here without building it)."""
+    return dtype == torch.bfloat16 and ((dim in (64, 128) and vdim in (64, 128)) or (dim, vdim) == (64, 48))
 
 
 def attention_prompt_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,

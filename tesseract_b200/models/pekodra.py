@@ -96,8 +96,13 @@ def pekodra_kernel_libraries(cfg: PekodraConfig, dtype: str):
         shared.append("experts")
     if any(layer.mlp is None for layer in cfg.layers):
         shared.append("norm")          # a single pending update goes through the grouped norm's own kernel
-    if dtype != "float32" and any(layer.mixer.dim in (64, 128) and layer.mixer.vdim in (48, 64, 128) for layer in cfg.layers):
-        shared.append("attention_prompt_mma")     # (head sizes the tensor-core prompt attention may take)
+    if dtype != "float32":
+        import torch
+
+        from .. import kernels
+
+        if any(kernels.attention_prompt_mma_supported(torch.bfloat16, layer.mixer.dim, layer.mixer.vdim) for layer in cfg.layers):
+            shared.append("attention_prompt_mma")     # (head sizes the tensor-core attention takes)
     return shared + (["gemm_f32"] if dtype == "float32" else ["decode_linear", "skinny_tcgen05"])
 
 

@@ -866,3 +866,14 @@ def test_random_configurations_match_plain_in_bfloat16(tmp_path, seed):
         stepper = make_stepper(model, capacity_tokens=max(1024, max_live_tokens(steps)), max_requests=4)
         replay_against_plain(stepper, steps, folder, requests, "bfloat16", f"seed {seed}/{name}", measured_noise=True)
         assert stepper.cache.used_pages() == 0
+
+
+def test_the_library_and_the_plan_agree_on_the_tensor_core_head_sizes():
+    from tesseract_b200 import kernels
+    from tesseract_b200.csrc.build import load_library
+
+    lib = load_library("attention_prompt_mma")
+    for d in (8, 16, 48, 64, 96, 128, 256):
+        for dv in (8, 48, 64, 96, 128, 256):
+            assert bool(lib.tb_attention_prompt_mma_supported(d, dv)) == kernels.attention_prompt_mma_supported(torch.bfloat16, d, dv)
+    assert not kernels.attention_prompt_mma_supported(torch.float32, 64, 64)
